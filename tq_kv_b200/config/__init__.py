@@ -1,5 +1,8 @@
 """Typed configuration, the architecture registry and the named shapes."""
 from .model_spec import ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .pavisun import ARCHITECTURE as PAVISUN_ARCHITECTURE
+from .pavisun import MODEL_TYPE as PAVISUN_MODEL_TYPE
+from .pavisun import PavisunConfig, build_pavisun_spec
 from .qwen2 import ARCHITECTURE as QWEN2_ARCHITECTURE
 from .qwen2 import MODEL_TYPE as QWEN2_MODEL_TYPE
 from .qwen2 import Qwen2Config, build_qwen2_spec, read_config_json
@@ -22,7 +25,11 @@ register_architecture(
 register_architecture(
     Architecture(RIRUDRA_ARCHITECTURE, RIRUDRA_MODEL_TYPE, RirudraConfig, build_rirudra_spec), replace=True)
 
+register_architecture(
+    Architecture(PAVISUN_ARCHITECTURE, PAVISUN_MODEL_TYPE, PavisunConfig, build_pavisun_spec), replace=True)
+
 __all__ = [
+    "PavisunConfig", "build_pavisun_spec",
     "RirudraConfig", "build_rirudra_spec",
     "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "ScheduleEntry",
     "ZodosunConfig", "build_zodosun_spec",

@@ -84,6 +84,9 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: tuple[int, ...] = ()
+    # > 0: the residual stream is kept as this many parallel streams (parts/residual_streams.py); the layers are
+    # then blocks that work on streams, and the final norm reads the streams' sum
+    residual_streams: int = 0
 
     def validate(self) -> None:
         n = len(self.layers)

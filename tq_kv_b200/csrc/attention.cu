@@ -8,6 +8,11 @@
 // q·k / sqrt(head_dim) of q head h against kv head h / n_rep, keys after the
 // query masked (-inf), softmax over keys, times V.  The window (not in the
 // reference) lets the query at position p see keys max(0, p-window+1) .. p.
+//
+// Options beyond the reference (AttnOptions; all off by default): value rows
+// of another width than the keys; a cap on the scores, s <- cap * tanh(s / cap);
+// a bias that grows with the distance, s <- s - slope[h] * (p - j); and first
+// tokens that stay visible behind the window (keys j < keep_first).
 #include "common.cuh"
 
 #define ATT_MAX_PAIRS 8   // head_dim <= 512: each lane owns up to 8 pairs of dims
@@ -25,20 +30,27 @@ struct KVSource {
     int page_tokens;
 };
 
+struct AttnOptions {
+    int vd;                 // width of a value row (the keys' width hd if they are alike)
+    float softcap;          // > 0: scores become softcap * tanh(score / softcap)
+    const float* slopes;    // [nh] or null: score -= slopes[h] * (query position - key position)
+    int keep_first;         // with a window: keys below this position stay visible
+};
+
 template <typename TC>
-__device__ __forceinline__ void kv_rows(const KVSource& src, int b, int j, int g, int nkv, int hd, int tok0,
+__device__ __forceinline__ void kv_rows(const KVSource& src, int b, int j, int g, int nkv, int hd, int vd, int tok0,
                                         const TC*& krow, const TC*& vrow) {
     if (src.k_packed) {
-        const size_t r = ((size_t)(tok0 + j) * nkv + g) * hd;
-        krow = (const TC*)src.k_packed + r;
-        vrow = (const TC*)src.v_packed + r;
+        const size_t r = (size_t)(tok0 + j) * nkv + g;
+        krow = (const TC*)src.k_packed + r * hd;
+        vrow = (const TC*)src.v_packed + r * vd;
     } else {
         int lp = j / src.page_tokens;
         if (src.ring_pages > 0) lp %= src.ring_pages;
         const int page = src.block_table[(size_t)b * src.table_width + lp];
-        const size_t r = (((size_t)page * nkv + g) * src.page_tokens + (j % src.page_tokens)) * hd;
-        krow = (const TC*)src.k_pages + r;
-        vrow = (const TC*)src.v_pages + r;
+        const size_t r = ((size_t)page * nkv + g) * src.page_tokens + (j % src.page_tokens);
+        krow = (const TC*)src.k_pages + r * hd;
+        vrow = (const TC*)src.v_pages + r * vd;
     }
 }
 
@@ -49,7 +61,7 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
                                  const int* __restrict__ tok_seq, const int* __restrict__ cu_seqlens,
                                  const int* __restrict__ start_pos, int window, float scale, TC* __restrict__ out,
                                  float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv, int hd,
-                                 int n_splits) {
+                                 int n_splits, AttnOptions opt) {
     extern __shared__ float q_sh[];   // [n_warps][hd]
     const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -58,12 +70,16 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
     const int b = tok_seq[t];
     const int tok0 = src.k_packed ? cu_seqlens[b] - start_pos[b] : 0;
     const int lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    int lo = lo_all, hi = pos + 1;                      // [lo, hi): this block's keys
+    // The visible keys, counted 0 .. n_keys-1: first the kept first tokens that the window has left behind
+    // (n_keep of them, positions 0 .. n_keep-1), then the window's keys lo_all .. pos.
+    const int n_keep = opt.keep_first < lo_all ? opt.keep_first : lo_all;
+    const int n_keys = n_keep + pos + 1 - lo_all;
+    const int vd = opt.vd;
+    int lo = 0, hi = n_keys;                            // [lo, hi): this block's keys, in that count
     if (n_splits > 1) {
         // every token cuts its own key range into n_splits equal parts (multiples of 32 keys)
-        const int keys = pos + 1 - lo_all;
-        const int split_len = (((keys + n_splits - 1) / n_splits) + 31) & ~31;
-        lo = lo_all + split * split_len;
+        const int split_len = (((n_keys + n_splits - 1) / n_splits) + 31) & ~31;
+        lo = split * split_len;
         if (lo + split_len < hi) hi = lo + split_len;
     }
     float* qs = q_sh + warp * hd;
@@ -82,12 +98,13 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
         for (int i = 0; i < 2 * ATT_MAX_PAIRS; ++i) acc[i] = 0.f;
 
         for (int base = lo; base < hi; base += 32) {
-            const int j = base + lane;
-            const bool valid = j < hi;
+            const int c = base + lane;
+            const bool valid = c < hi;
+            const int j = c < n_keep ? c : lo_all + (c - n_keep);      // the key's position
             const TC *krow = nullptr, *vrow = nullptr;
             float s = -INFINITY;
             if (valid) {
-                kv_rows<TC>(src, b, j, g, nkv, hd, tok0, krow, vrow);
+                kv_rows<TC>(src, b, j, g, nkv, hd, vd, tok0, krow, vrow);
                 float dot = 0.f;
                 for (int d = 0; d < hd; d += VEC) {
                     float kv[VEC];
@@ -96,6 +113,8 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
                     for (int e = 0; e < VEC; ++e) dot = fmaf(qs[d + e], kv[e], dot);
                 }
                 s = dot * scale;
+                if (opt.softcap > 0.f) s = opt.softcap * tanhf(s / opt.softcap);
+                if (opt.slopes) s -= opt.slopes[h] * (float)(pos - j);
             }
             const float m_new = fmaxf(m, warp_max(s));       // finite: lane 0 of a chunk is always valid
             const float p = valid ? expf(s - m_new) : 0.f;
@@ -111,7 +130,7 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
 #pragma unroll
                 for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
                     const int d = 2 * lane + 64 * i;
-                    if (d < hd) {
+                    if (d < vd) {
                         const float2 vv = load2_f32<TC>(vr + d);
                         acc[2 * i] = fmaf(pj, vv.x, acc[2 * i]);
                         acc[2 * i + 1] = fmaf(pj, vv.y, acc[2 * i + 1]);
@@ -122,19 +141,19 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
 
         if (n_splits == 1) {
             const float inv = 1.f / l;
-            TC* o = out + ((size_t)t * nh + h) * hd;
+            TC* o = out + ((size_t)t * nh + h) * vd;
 #pragma unroll
             for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
                 const int d = 2 * lane + 64 * i;
-                if (d < hd) store2_f32<TC>(o + d, acc[2 * i] * inv, acc[2 * i + 1] * inv);
+                if (d < vd) store2_f32<TC>(o + d, acc[2 * i] * inv, acc[2 * i + 1] * inv);
             }
         } else {
             const size_t r = ((size_t)t * nh + h) * n_splits + split;
-            float* pa = part_acc + r * hd;
+            float* pa = part_acc + r * vd;
 #pragma unroll
             for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
                 const int d = 2 * lane + 64 * i;
-                if (d < hd) store2_f32<float>(pa + d, acc[2 * i], acc[2 * i + 1]);
+                if (d < vd) store2_f32<float>(pa + d, acc[2 * i], acc[2 * i + 1]);
             }
             if (lane == 0) { part_ml[2 * r] = m; part_ml[2 * r + 1] = l; }
         }
@@ -175,18 +194,23 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     }
 }
 
-// Scratch needed for n_splits > 1: part_acc float[T*nh*n_splits*hd], part_ml float[T*nh*n_splits*2].
-TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const void* v_packed, const void* k_pages,
-                        const void* v_pages, const int* block_table, int table_width, int ring_pages,
-                        int page_tokens, const int* tok_pos, const int* tok_seq, const int* cu_seqlens,
-                        const int* start_pos, int window, float scale, void* out, float* part_acc, float* part_ml,
-                        int n_tokens, int nh, int nkv, int hd, int n_splits, cudaStream_t stream) {
+// Scratch needed for n_splits > 1: part_acc float[T*nh*n_splits*vd], part_ml float[T*nh*n_splits*2].
+// hd and vd: multiples of 8 up to 512 (rows of the cache then start on 16-byte boundaries in either precision).
+TQ_API int tq_attention_ext(const void* q, int dtype, const void* k_packed, const void* v_packed, const void* k_pages,
+                            const void* v_pages, const int* block_table, int table_width, int ring_pages,
+                            int page_tokens, const int* tok_pos, const int* tok_seq, const int* cu_seqlens,
+                            const int* start_pos, int window, float scale, void* out, float* part_acc, float* part_ml,
+                            int n_tokens, int nh, int nkv, int hd, int vd, float softcap, const float* slopes,
+                            int keep_first, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd <= 0 || hd > 64 * ATT_MAX_PAIRS || hd % 16 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (hd <= 0 || hd > 64 * ATT_MAX_PAIRS || hd % 8 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (vd <= 0 || vd > 64 * ATT_MAX_PAIRS || vd % 8 || keep_first < 0) return (int)cudaErrorInvalidValue;
+    if (keep_first > 0 && ring_pages > 0) return (int)cudaErrorInvalidValue;   // a ring has overwritten them
     if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
     if (!k_packed && (!k_pages || !block_table || page_tokens <= 0)) return (int)cudaErrorInvalidValue;
     if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorInvalidValue;
     KVSource src{k_packed, v_packed, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens};
+    AttnOptions opt{vd, softcap, slopes, window > 0 ? keep_first : 0};
     const int n_rep = nh / nkv;
     const int n_warps = n_rep < 8 ? n_rep : 8;
     const dim3 grid(n_tokens, nkv, n_splits);
@@ -194,21 +218,32 @@ TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const vo
     if (dtype == TQ_F32)
         attention_kernel<float><<<grid, n_warps * 32, smem, stream>>>(
             (const float*)q, src, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, (float*)out, part_acc,
-            part_ml, nh, nkv, hd, n_splits);
+            part_ml, nh, nkv, hd, n_splits, opt);
     else if (dtype == TQ_BF16)
         attention_kernel<bf16><<<grid, n_warps * 32, smem, stream>>>(
             (const bf16*)q, src, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, (bf16*)out, part_acc,
-            part_ml, nh, nkv, hd, n_splits);
+            part_ml, nh, nkv, hd, n_splits, opt);
     else
         return (int)cudaErrorInvalidValue;
     int st = tq_launch_status();
     if (st || n_splits == 1) return st;
     const dim3 mgrid(n_tokens, nh);
     if (dtype == TQ_F32)
-        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, hd, n_splits);
+        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, vd, n_splits);
     else
-        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, hd, n_splits);
+        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, vd, n_splits);
     return tq_launch_status();
+}
+
+TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const void* v_packed, const void* k_pages,
+                        const void* v_pages, const int* block_table, int table_width, int ring_pages,
+                        int page_tokens, const int* tok_pos, const int* tok_seq, const int* cu_seqlens,
+                        const int* start_pos, int window, float scale, void* out, float* part_acc, float* part_ml,
+                        int n_tokens, int nh, int nkv, int hd, int n_splits, cudaStream_t stream) {
+    if (hd % 16) return (int)cudaErrorInvalidValue;
+    return tq_attention_ext(q, dtype, k_packed, v_packed, k_pages, v_pages, block_table, table_width, ring_pages,
+                            page_tokens, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, out, part_acc,
+                            part_ml, n_tokens, nh, nkv, hd, hd, 0.f, nullptr, 0, n_splits, stream);
 }
 
 // The merge step alone, for kernels that write (unnormalised output, max, sum) per split themselves.

@@ -217,7 +217,8 @@ template <int EPI, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias, int M, int N, int K,
-               int b_rows_second, int n_whole, int parts, int* __restrict__ status) {
+               int b_rows_second, int n_whole, int parts, int* __restrict__ status,
+               const int* __restrict__ tile_b_row) {
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -287,6 +288,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int t, k_lo, k_iters, part;
                 item(w, t, k_lo, k_iters, part);
                 const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
+                const int b_base = tile_b_row ? tile_b_row[t % tiles_m] : 0;
+                if (b_base < 0) continue;                       // a tile of rows that nobody owns
                 for (int i = 0; i < k_iters; ++i, ++it) {
                     const int s = it % TC_STAGES;
                     if (!mbar_wait(smem_u32(&empty[s]), ((it / TC_STAGES) & 1) ^ 1)) { *failed = 1; ok = false; break; }
@@ -297,10 +300,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int kc = (k_lo + i) * TC_BK;
                     tma_load_2d(a_dst, &map_a, kc, m0, fb);
                     if (EPI == EPI_SWIGLU) {
-                        tma_load_2d(b_dst, &map_b, kc, n0, fb);                                  // gate rows
-                        tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, kc, b_rows_second + n0, fb); // up rows
+                        tma_load_2d(b_dst, &map_b, kc, b_base + n0, fb);                                  // gate rows
+                        tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, kc, b_base + b_rows_second + n0, fb); // up rows
                     } else {
-                        tma_load_2d(b_dst, &map_b, kc, n0, fb);
+                        tma_load_2d(b_dst, &map_b, kc, b_base + n0, fb);
                     }
                 }
             }
@@ -311,11 +314,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = instr_desc(TC_BM, TC_BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
                 int t, k_lo, k_iters, part;
                 item(w, t, k_lo, k_iters, part);
+                if (tile_b_row && tile_b_row[t % tiles_m] < 0) continue;       // (`local` counts live tiles only)
                 const uint32_t buf = local & 1;
                 if (!mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) & 1) ^ 1)) { *failed = 1; ok = false; break; }
+                ++local;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * TC_BN;
                 for (int i = 0; i < k_iters; ++i, ++it) {
@@ -346,12 +351,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         unsigned char* st = staging + (warp - 2) * 2 * TC_EPI_BYTES;
         uint32_t local = 0, piece = 0;
         bool ok = true;
-        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
             int t, k_lo, k_iters, part;
             item(w, t, k_lo, k_iters, part);
+            if (tile_b_row && tile_b_row[t % tiles_m] < 0) continue;
             const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * OUT_COLS;
             const uint32_t buf = local & 1;
             if (!mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1, true)) { *failed = 1; ok = false; break; }
+            ++local;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TC_BN;
             const int row0 = m0 + quarter * 32;
@@ -635,7 +642,26 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     const int n_items = n_whole + (n_tiles - n_whole) * parts;
     const int grid = n_items < sm_count ? n_items : sm_count;
     return tq_launch_pdl(TQ_PDL_GEMM_TC, gemm_tc_kernel<EPI, TO>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, ma, mb,
-                         mc, bias, M, N, K, b_rows_second, n_whole, parts, status);
+                         mc, bias, M, N, K, b_rows_second, n_whole, parts, status, (const int*)nullptr);
+}
+
+// The grouped form: every 128-row tile of A has a B of its own (tile_b_row, see tq_gemm_tc_grouped); whole tiles only.
+template <int EPI, typename TO>
+static int launch_tc_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K,
+                             int b_rows_second, const int* tile_b_row, int* status, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             TC_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
+    const int sm_count = tc_sm_count();
+    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
+    return tq_launch_pdl(TQ_PDL_GEMM_TC, gemm_tc_kernel<EPI, TO>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, ma, mb,
+                         mc, (const float*)nullptr, M, N, K, b_rows_second, n_tiles, 1, status, tile_b_row);
 }
 
 // The pair form: 256-row tiles on clusters of two blocks.
@@ -725,4 +751,36 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     if (epilogue == EPI_SWIGLU && c_dtype == TQ_BF16) TQ_TC(EPI_SWIGLU, bf16);
 #undef TQ_TC
     return (int)cudaErrorInvalidValue;
+}
+
+// Many products in one launch: the rows of A come in tiles of 128, and tile i multiplies with the rows
+// tile_b_row[i] .. of B (device int32 [ceil(M / 128)]; a negative entry: the tile is skipped and its rows of
+// C stay as they are).  B [b_rows, K] stacks the groups' matrices; with epilogue 2 a group's block holds its
+// gate rows and, b_rows_second rows further on, its up rows.  C [M, N]: columns past N are never written, so a
+// tile may reach into the next group's rows of B.  Epilogues 0 (store) and 2 (SwiGLU); other rules as tq_gemm_tc.
+TQ_API int tq_gemm_tc_grouped(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
+                              int ldc, int epilogue, int b_rows, int b_rows_second, const int* tile_b_row, int* status,
+                              cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || !tile_b_row || b_rows <= 0) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+        return (int)cudaErrorInvalidValue;
+    if (c_dtype != TQ_F32 && c_dtype != TQ_BF16) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || ((size_t)ldc * (c_dtype == TQ_F32 ? 4 : 2)) % 16)
+        return (int)cudaErrorInvalidValue;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return (int)cudaErrorInvalidValue;
+    CUtensorMap ma, mb, mc;
+    int st = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM);
+    if (st) return st;
+    st = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)K, (uint64_t)ldb, epilogue == EPI_SWIGLU ? TC_BN / 2 : TC_BN);
+    if (st) return st;
+    st = make_map_c(&mc, C, c_dtype == TQ_F32, (uint64_t)M, (uint64_t)N, (uint64_t)ldc);
+    if (st) return st;
+    if (epilogue == EPI_STORE && c_dtype == TQ_F32)
+        return launch_tc_grouped<EPI_STORE, float>(ma, mb, mc, M, N, K, 0, tile_b_row, status, stream);
+    if (epilogue == EPI_STORE)
+        return launch_tc_grouped<EPI_STORE, bf16>(ma, mb, mc, M, N, K, 0, tile_b_row, status, stream);
+    if (c_dtype == TQ_F32)
+        return launch_tc_grouped<EPI_SWIGLU, float>(ma, mb, mc, M, N, K, b_rows_second, tile_b_row, status, stream);
+    return launch_tc_grouped<EPI_SWIGLU, bf16>(ma, mb, mc, M, N, K, b_rows_second, tile_b_row, status, stream);
 }

@@ -17,6 +17,7 @@ from ..cache import KVLayerView, KVRequest, SequenceCache, StateRequest
 from ..config import ConfigError, ModelSpec
 from ..parts import Runtime, StepBatch, StepContext, WeightSpec, make_block, make_part
 from ..parts.base import shapes_agree
+from ..parts.residual_streams import ResidualStreams
 
 
 class DecoderModel:
@@ -110,6 +111,8 @@ class DecoderModel:
             h = self.embedding.forward(batch.tokens, batch.tok_pos)
         else:
             h = self.embedding.forward(batch.tokens)
+        if self.spec.residual_streams > 0:
+            h = ResidualStreams(h, self.spec.residual_streams)
         kernels.mark("embed")
         for i, e in enumerate(self.spec.schedule):
             owner = i if e.cache_of is None else e.cache_of
@@ -124,7 +127,10 @@ class DecoderModel:
             self.blocks[e.layer].forward(h, ctx)
         if batch.n_logit_rows == 0:
             return None
-        normed = self.final_norm.forward(h, rt.act_dtype, rows=batch.logit_rows)
+        if isinstance(h, ResidualStreams):
+            normed = h.read_sum(self.final_norm.weight, self.final_norm.eps, rt.act_dtype, rows=batch.logit_rows)
+        else:
+            normed = self.final_norm.forward(h, rt.act_dtype, rows=batch.logit_rows)
         logits = self.head.forward(normed)
         kernels.mark("head")
         return logits

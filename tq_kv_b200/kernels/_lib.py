@@ -213,6 +213,25 @@ _SIGNATURES = {
     "tq_sigmoid_flash_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                 c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sigmoid_attention_sum": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_attention_ext": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
+    "tq_head_encode": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tq_tanh_cap": [c_void_p, c_size_t, c_float, c_void_p],
+    "tq_streams_step": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                        c_void_p, c_int, c_void_p, c_int, c_void_p],
+    "tq_streams_fill": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
+    "tq_table_choice": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "tq_routed_experts_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                               c_void_p, c_void_p, c_int, c_void_p],
+    "tq_routed_sort": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_void_p],
+    "tq_routed_combine": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "tq_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_void_p, c_void_p, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
                   c_void_p, c_void_p],
     "tq_sample_seeded": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, ctypes.c_ulonglong, c_int,

@@ -115,3 +115,65 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
         int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, head_dim,
         n_splits, stream()), "attention", 2 if n_splits > 1 else 1)
     return out
+
+
+def check_row_widths(n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int) -> None:
+    """Raises for head sizes the general attention kernel with options does not take."""
+    for name, d in (("key", key_dim), ("value", value_dim)):
+        if d % 8 or not 8 <= d <= MAX_HEAD_DIM:
+            raise KernelError(f"attention: the {name} rows' width {d} must be a multiple of 8 between 8 and {MAX_HEAD_DIM}")
+    if n_kv_heads <= 0 or n_heads % n_kv_heads or n_kv_heads > 65535:
+        raise KernelError(f"attention: {n_heads} heads cannot be shared among {n_kv_heads} key/value heads")
+
+
+def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int,
+                  value_dim: int, tok_pos: torch.Tensor, tok_seq: torch.Tensor, cu_seqlens: torch.Tensor,
+                  start_pos: torch.Tensor, scale: float, window: Optional[int] = None, keep_first: int = 0,
+                  softcap: Optional[float] = None, slopes: Optional[torch.Tensor] = None,
+                  k_packed: Optional[torch.Tensor] = None, v_packed: Optional[torch.Tensor] = None,
+                  k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                  block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
+                  page_tokens: int = 64, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
+                  use_fast: bool = True):
+    """Softmax attention with options: for the query at position i of head h and the key at position j <= i,
+
+        s = q . k * scale;   s <- softcap * tanh(s / softcap)  (if a cap is given);
+        s <- s - slopes[h] * (i - j)                            (if slopes are given);
+
+    j is visible if i - j < window or j < keep_first (no window: every j <= i).  Value rows may have another
+    width than the keys.  q [T, nh*key_dim], out [T, nh*value_dim]; keys and values as in `attention`."""
+    check_row_widths(n_heads, n_kv_heads, key_dim, value_dim)
+    T = q.shape[0]
+    if q.shape[1] != n_heads * key_dim or tuple(out.shape) != (T, n_heads * value_dim) or out.dtype != q.dtype:
+        raise KernelError("attention: q must be [T, n_heads*key_dim] and out [T, n_heads*value_dim] of one dtype")
+    packed = k_packed is not None
+    if packed:
+        if (v_packed is None or k_packed.dtype != q.dtype or tuple(k_packed.shape) != (T, n_kv_heads * key_dim)
+                or tuple(v_packed.shape) != (T, n_kv_heads * value_dim)):
+            raise KernelError("attention: packed keys [T, n_kv_heads*key_dim] and values [T, n_kv_heads*value_dim] of q's dtype")
+    else:
+        if k_pages is None or v_pages is None or block_table is None or k_pages.dtype != q.dtype:
+            raise KernelError("attention: no key/value source of q's dtype was given")
+        if (tuple(k_pages.shape[1:]) != (n_kv_heads, page_tokens, key_dim)
+                or tuple(v_pages.shape[1:]) != (n_kv_heads, page_tokens, value_dim)):
+            raise KernelError(f"attention: cache pages have shapes {tuple(k_pages.shape)} / {tuple(v_pages.shape)}")
+    if slopes is not None and (slopes.dtype != torch.float32 or tuple(slopes.shape) != (n_heads,)):
+        raise KernelError("attention: slopes must be float32 [n_heads]")
+    if keep_first and ring_pages:
+        raise KernelError("attention: kept first tokens need a cache that keeps all keys")
+    part_acc = part_ml = None
+    if n_splits > 1:
+        need = split_scratch_floats(T, n_heads, value_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention: {n_splits} splits need {need} float32 of scratch")
+        n_acc = T * n_heads * n_splits * value_dim
+        part_acc, part_ml = scratch[:n_acc], scratch[n_acc:need]
+    need_contiguous(q=q, out=out, k_packed=k_packed, v_packed=v_packed, k_pages=k_pages, v_pages=v_pages,
+                    block_table=block_table, slopes=slopes)
+    check(core().tq_attention_ext(
+        ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
+        table_width, ring_pages, page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos),
+        int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim,
+        value_dim, float(softcap or 0.0), ptr(slopes), int(keep_first) if window else 0, n_splits, stream()),
+        "attention_ext", 2 if n_splits > 1 else 1)
+    return out

@@ -208,3 +208,55 @@ def scale_inplace(x: torch.Tensor, s: float):
     need_contiguous(x=x)
     check(core().tq_scale_inplace(ptr(x), x.numel(), float(s), stream()), "scale_inplace")
     return x
+
+
+def head_encode(proj: torch.Tensor, ctx_pos, q_out: torch.Tensor, *, q_col: int, k_col: int, v_col: int,
+                n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, cos=None, sin=None, rotary_dim: int = 0,
+                norm_eps: float = 0.0, k_out=None, v_out=None, k_pages=None, v_pages=None, block_table=None,
+                table_width: int = 0, ring_pages: int = 0, page_tokens: int = 64):
+    """From projected float32 rows [T, ld] (q heads from column q_col, k heads from k_col, v heads from v_col; with
+    v_col < 0 the values are the keys as projected) to encoded q, and k / v packed and / or appended to the cache
+    (see csrc/head_encode.cu).  `ctx_pos` = (tok_pos, tok_seq, new_lens).  q and k are rotated over their first
+    `rotary_dim` entries (cos/sin float32 [positions, rotary_dim/2]) or, with norm_eps > 0, divided by their root
+    mean square per head."""
+    tok_pos, tok_seq, new_lens = ctx_pos
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelError("head_encode: the projected rows must be float32")
+    if rotary_dim:
+        if rotary_dim % 2 or rotary_dim > key_dim or cos is None or cos.dtype != torch.float32 \
+                or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"head_encode: rotary_dim {rotary_dim} needs float32 tables [positions, {rotary_dim // 2}]")
+    if v_col < 0 and value_dim != key_dim:
+        raise KernelError("head_encode: values that are the keys have the keys' width")
+    need = max(q_col + n_heads * key_dim, k_col + n_kv_heads * key_dim, v_col + n_kv_heads * value_dim if v_col >= 0 else 0)
+    if need > ld or min(q_col, k_col) < 0:
+        raise KernelError(f"head_encode: the columns reach {need}, the rows have {ld}")
+    for t in (k_out, v_out, k_pages, v_pages):
+        if t is not None and t.dtype != q_out.dtype:
+            raise KernelError("head_encode: all outputs and the cache must share one dtype")
+    need_contiguous(q_out=q_out, k_out=k_out, v_out=v_out, k_pages=k_pages, v_pages=v_pages, block_table=block_table,
+                    cos=cos, sin=sin)
+    check(core().tq_head_encode(ptr(proj), proj.stride(0), q_col, k_col, v_col, ptr(cos), ptr(sin), rotary_dim,
+                                float(norm_eps), ptr(tok_pos), ptr(tok_seq), ptr(new_lens), ptr(block_table),
+                                table_width, ring_pages, page_tokens, ptr(q_out), ptr(k_out), ptr(v_out), ptr(k_pages),
+                                ptr(v_pages), dtype_code(q_out), T, n_heads, n_kv_heads, key_dim, value_dim, stream()),
+          "head_encode")
+    return q_out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor):
+    """x[t, i] *= sigmoid(gate[t, i]) in place; gate float32, possibly a column slice of wider rows."""
+    T, n = x.shape
+    if gate.dtype != torch.float32 or tuple(gate.shape) != (T, n) or gate.stride(1) != 1 or not x.is_contiguous():
+        raise KernelError("sigmoid_gate: gate must be float32 of x's shape, x contiguous")
+    check(core().tq_sigmoid_gate(ptr(x), dtype_code(x), ptr(gate), gate.stride(0), T, n, stream()), "sigmoid_gate")
+    return x
+
+
+def tanh_cap(x: torch.Tensor, cap: float):
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("tanh_cap: x must be contiguous float32")
+    check(core().tq_tanh_cap(ptr(x), x.numel(), float(cap), stream()), "tanh_cap")
+    return x

@@ -14,6 +14,9 @@ from .position import RotaryHalved, RotaryTables
 from .side_by_side import SideBySideMixer
 from .sigmoid_attention import SigmoidAttention
 from .state_space import StateSpaceMixer
+from .residual_streams import ResidualStreams, StreamConnection, StreamsBlock
+from .routed_experts import TableExperts
+from .softmax_attention import SoftmaxAttention
 from .registry import make_block, make_part, part_kinds, register_block, register_part, unregister_part
 
 register_part("rms_norm", RMSNorm, replace=True)
@@ -28,13 +31,17 @@ register_part("latent_attention", LatentAttention, replace=True)
 register_part("state_space_mixer", StateSpaceMixer, replace=True)
 register_part("gated_delta_mixer", GatedDeltaMixer, replace=True)
 register_part("gqa_attention", GQAttention, replace=True)
+register_part("softmax_attention", SoftmaxAttention, replace=True)
+register_part("table_experts", TableExperts, replace=True)
+register_part("stream_connection", StreamConnection, replace=True)
 register_part("swiglu", SwiGLU, replace=True)
 register_part("token_embedding", TokenEmbedding, replace=True)
 register_part("lm_head", LMHead, replace=True)
 register_block("prenorm_residual", PrenormResidualBlock, replace=True)
 register_block("parallel_residual", ParallelResidualBlock, replace=True)
+register_block("residual_streams", StreamsBlock, replace=True)
 
-__all__ = ["GatedDeltaMixer", "LatentAttention", "ParallelResidualBlock", "RotaryTables", "StateSpaceMixer", "DecayedStateMixer", "DeltaRuleMixer", "GroupRMSNorm", "SideBySideMixer", "SigmoidAttention",
+__all__ = ["ResidualStreams", "SoftmaxAttention", "StreamConnection", "StreamsBlock", "TableExperts", "GatedDeltaMixer", "LatentAttention", "ParallelResidualBlock", "RotaryTables", "StateSpaceMixer", "DecayedStateMixer", "DeltaRuleMixer", "GroupRMSNorm", "SideBySideMixer", "SigmoidAttention",
            "FeedForward", "GQAttention", "LMHead", "Mixer", "Norm", "Part", "PositionEncoding",
            "PrenormResidualBlock", "RMSNorm", "RotaryHalved", "Runtime", "StepBatch", "StepContext", "SwiGLU",
            "TokenEmbedding", "WeightSpec", "float32_vector", "make_block", "make_part", "part_kinds",

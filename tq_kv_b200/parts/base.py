@@ -102,6 +102,9 @@ class StepContext:
     entry: int                              # index of the running schedule entry
     kv: Optional[KVLayerView] = None        # cache of this entry (or of the entry it reads)
     state: Optional[torch.Tensor] = None    # [max_slots, *shape] state of this entry, indexed by slot
+    # True: the part's result REPLACES what `residual` holds (a buffer of its own that need not be cleared) instead
+    # of being added to it.  A block sets it only for a part that says `can_store_result`.
+    store_result: bool = False
 
 
 class Part:
@@ -119,6 +122,8 @@ class Part:
     # A mixer or feed-forward that hands its input to `kernels.linear` and reads it nowhere else may set this:
     # the block then passes the norm before it as a `kernels.PendingNorm`, which the product can fold in.
     takes_pending_norm = False
+    # A mixer or feed-forward that honours StepContext.store_result (see there).
+    can_store_result = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

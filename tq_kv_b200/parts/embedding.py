@@ -66,6 +66,8 @@ class LMHead(Part):
         self.tied_to = self.params.get("tied_to")
         self.weight_name = self.params.get("weight_name") or self.prefix + "weight"
         self.logit_scale = float(self.params.get("logit_scale", 1.0))     # the logits are multiplied by it
+        cap = self.params.get("logit_softcap")                            # then capped: cap * tanh(logits / cap)
+        self.logit_softcap = float(cap) if cap else None
         self.weight = None
 
     def weight_specs(self):
@@ -84,4 +86,6 @@ class LMHead(Part):
         logits = kernels.linear(normed_rows, self.weight, out_dtype=torch.float32)
         if self.logit_scale != 1.0:
             kernels.scale_inplace(logits, self.logit_scale)
+        if self.logit_softcap is not None:
+            kernels.tanh_cap(logits, self.logit_softcap)
         return logits

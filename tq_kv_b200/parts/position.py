@@ -66,10 +66,17 @@ class RotaryHalved(PositionEncoding):
 
 
 class RotaryTables(PositionEncoding):
-    """Cosines and sines of the angles pos * theta^(-2i / rotary_dim), i < rotary_dim / 2, for mixers whose own
-    kernels turn their vectors (`layout` says how the mixer pairs entries: "pairs" turns entry 2i with 2i + 1,
-    "halves" entry i with i + rotary_dim / 2).  The angles are formed in float64 on the host and their cosines
-    and sines rounded once to float32, so that the tables carry no error that grows with the position."""
+    """Cosines and sines of the angles pos * rate_i, i < rotary_dim / 2, for mixers whose own kernels turn their
+    vectors (`layout` says how the mixer pairs entries: "pairs" turns entry 2i with 2i + 1, "halves" entry i with
+    i + rotary_dim / 2).  The angles are formed in float64 on the host and their cosines and sines rounded once
+    to float32, so that the tables carry no error that grows with the position.
+
+    Plain rates are theta^(-2i / rotary_dim).  With `scaling` = {factor F, original L, fast, slow} the slow
+    pairs are stretched for contexts longer than the L positions the rates were made for: a pair that makes t
+    turns over L positions has index n(t) = rotary_dim * ln(L / (2 pi t)) / (2 ln theta); with
+    lo = max(floor(n(fast)), 0) and hi = min(ceil(n(slow)), rotary_dim - 1), pair i takes the share
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) of the rate divided by F and 1 - r_i of its own rate,
+    and cosines and sines are multiplied by 0.1 ln F + 1 (the tables carry that factor)."""
     padded_rows_ok = True
 
     def __init__(self, spec):
@@ -79,6 +86,12 @@ class RotaryTables(PositionEncoding):
         self.layout = self.params.get("layout", "pairs")
         if self.layout not in ("pairs", "halves") or self.rotary_dim % 2:
             raise ValueError(f"rotary tables: layout '{self.layout}' (pairs or halves), an even rotary_dim")
+        sc = self.params.get("scaling")
+        self.scaling = None
+        if sc:
+            self.scaling = (float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
+            if min(self.scaling) <= 0.0:
+                raise ValueError(f"rotary tables: scaling needs positive factor, original, fast and slow, not {sc}")
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
 
@@ -86,17 +99,33 @@ class RotaryTables(PositionEncoding):
     def paired(self) -> bool:
         return self.layout == "pairs"
 
-    def prepare(self, runtime: Runtime, shared: Optional[dict] = None) -> None:
-        key = (("rotary_tables", self.rotary_dim, self.theta), runtime.max_context, str(runtime.device))
-        if shared is not None and key in shared:
-            self.cos, self.sin = shared[key]
-            return
+    def rates(self) -> tuple[torch.Tensor, float]:
+        """The float64 rates of the pairs and the factor on cosine and sine."""
         half = max(1, self.rotary_dim // 2)
         i = torch.arange(half, dtype=torch.float64)
         rate = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(2, self.rotary_dim))
+        if self.scaling is None:
+            return rate, 1.0
+        import math
+        F, L, fast, slow = self.scaling
+
+        def index_of(turns: float) -> float:
+            return self.rotary_dim * math.log(L / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(index_of(fast)), 0)
+        hi = min(math.ceil(index_of(slow)), self.rotary_dim - 1)
+        share = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return rate / F * share + rate * (1.0 - share), 0.1 * math.log(F) + 1.0
+
+    def prepare(self, runtime: Runtime, shared: Optional[dict] = None) -> None:
+        key = (("rotary_tables", self.rotary_dim, self.theta, self.scaling), runtime.max_context, str(runtime.device))
+        if shared is not None and key in shared:
+            self.cos, self.sin = shared[key]
+            return
+        rate, factor = self.rates()
         ang = torch.arange(runtime.max_context, dtype=torch.float64).reshape(-1, 1) * rate.reshape(1, -1)
-        self.cos = torch.cos(ang).to(torch.float32).contiguous().to(runtime.device)
-        self.sin = torch.sin(ang).to(torch.float32).contiguous().to(runtime.device)
+        self.cos = (torch.cos(ang) * factor).to(torch.float32).contiguous().to(runtime.device)
+        self.sin = (torch.sin(ang) * factor).to(torch.float32).contiguous().to(runtime.device)
         if shared is not None:
             shared[key] = (self.cos, self.sin)
 

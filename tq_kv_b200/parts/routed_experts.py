@@ -1,0 +1,84 @@
+"""A feed-forward of `experts` small SwiGLU layers of which each token uses `top`.
+
+Expert e is  W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),  no biases.  Which experts a
+token uses is `routing`:
+  "table"   there is no router: a table [vocab, top] of expert indices (the
+            entries of a row differ) names them by the token's id; each has the
+            weight 1 / top.
+The result is the weighted sum of the chosen experts' results.
+
+The experts' weights are stacked at bind time ([E, 2F, W] gate rows then up rows,
+and [E, W, F]).  Few rows (decoding) and the float32 path run every (token, expert)
+pair as a row-times-matrix product of its own (csrc/routed_experts.cu); many
+bfloat16 rows are sorted by expert and run as tiles of one matrix product per
+projection (`kernels.routed_experts_tiles`).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config import ConfigError
+from .base import FeedForward, Runtime, StepContext, WeightSpec
+
+
+class TableExperts(FeedForward):
+    padded_rows_ok = True               # row by row
+    can_store_result = True
+    TILE_MIN_ROWS = 65                  # from this many rows on, bfloat16 steps run the sorted tiles
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.n_experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.vocab = int(p["vocab_size"])
+        self.routing = p.get("routing", "table")
+        if self.routing != "table":
+            raise ConfigError(f"routed experts: unknown routing '{self.routing}' (known: table)")
+        if not 1 <= self.top <= self.n_experts:
+            raise ConfigError(f"routed experts: a token cannot use {self.top} of {self.n_experts} experts")
+        self.names = dict(p.get("names", {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table"}))
+        self.w_gate_up = self.w_down = self.table = None
+
+    def _e(self, e: int, which: str) -> str:
+        return f"{self.prefix}{self.names['expert'].format(e)}{self.names[which]}"
+
+    def weight_specs(self):
+        specs = []
+        for e in range(self.n_experts):
+            specs += [WeightSpec(self._e(e, "gate"), (self.inter, self.hidden), "matrix"),
+                      WeightSpec(self._e(e, "up"), (self.inter, self.hidden), "matrix"),
+                      WeightSpec(self._e(e, "down"), (self.hidden, self.inter), "matrix")]
+        specs.append(WeightSpec(self.prefix + self.names["table"], (self.vocab, self.top),
+                                f"choice_table:{self.n_experts}"))
+        return specs
+
+    def bind(self, tensors, runtime: Runtime, shared=None):
+        mats = [tensors[self._e(e, w)] for e in range(self.n_experts) for w in ("gate", "up", "down")]
+        if len({m.dtype for m in mats}) != 1:
+            mats = [m.to(torch.float32) for m in mats]
+        gu = [torch.cat([mats[3 * e], mats[3 * e + 1]], dim=0) for e in range(self.n_experts)]
+        self.w_gate_up = torch.stack(gu).contiguous()                                       # [E, 2F, W]
+        self.w_down = torch.stack([mats[3 * e + 2] for e in range(self.n_experts)]).contiguous()   # [E, W, F]
+        table = tensors[self.prefix + self.names["table"]]
+        if table.dtype != torch.int32:
+            raise ConfigError(f"routed experts: the table {self.prefix + self.names['table']} must hold integers")
+        lo, hi = int(table.min()), int(table.max())
+        if lo < 0 or hi >= self.n_experts:
+            raise ConfigError(f"routed experts: the table names experts {lo} .. {hi}; there are {self.n_experts}")
+        self.table = table.contiguous()
+
+    def forward(self, x, ctx: StepContext, residual):
+        choice = kernels.table_choice(ctx.batch.tokens, self.table, self.n_experts)
+        T = x.shape[0]
+        if (T >= self.TILE_MIN_ROWS and x.dtype == torch.bfloat16
+                and kernels.routed_tiles_ok(x, self.w_gate_up, self.w_down)):
+            kernels.routed_experts_tiles(x, self.w_gate_up, self.w_down, choice, residual,
+                                         accumulate=not ctx.store_result)
+        else:
+            kernels.routed_experts_rows(x, self.w_gate_up, self.w_down, choice, residual,
+                                        accumulate=not ctx.store_result)
+        kernels.mark("experts")

@@ -1,0 +1,183 @@
+"""Grouped-query softmax attention with options, every one a parameter:
+
+  values            "projected": v = W_v x;  "keys": there is no W_v, the values are
+                    the keys as projected, before any rotation
+  position          a `rotary_tables` part (layout "halves"): q and k are rotated over
+                    their first rotary_dim entries; None: no rotation
+  qk_norm_eps       q and k are divided per head by their root mean square,
+                    x / sqrt(mean(x^2) + eps), without a weight
+  scale             s = q . k * scale
+  softcap           s <- softcap * tanh(s / softcap)
+  slope_exponent    a bias that grows with the distance: s <- s - m_h * (i - j),
+                    m_h = 2^(-slope_exponent * (h + 1) / heads) for head h = 0 ..
+  window            the query at position i sees key j <= i if i - j < window
+  keep_first        ... or if j < keep_first (the first tokens stay visible; they keep
+                    their true positions)
+  output_gate       the heads side by side are multiplied entry by entry with
+                    sigmoid(W_g x) before the output projection
+Query head h reads key/value head h // (heads / kv_heads).  Key rows and value rows
+may differ in width.  No biases.
+
+All projections are one product with the concatenated weight (float32 result); one
+kernel encodes q and k, splits the heads and appends k and v to the cache
+(csrc/head_encode.cu).  Prompts from position 0 attend over the step's own keys;
+everything else reads the paged cache: a ring for a plain window, all keys where
+first tokens are kept (the kernels skip what lies between the kept tokens and the
+window).  Scores, softmax and the bias are float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..cache import PAGE_TOKENS, KVRequest, ring_pages_for
+from ..config import ConfigError
+from .base import Mixer, Runtime, StepContext, WeightSpec
+from .registry import make_part
+
+
+class SoftmaxAttention(Mixer):
+    padded_rows_ok = True               # causal: no row sees a later one; rows past a sequence's length are not cached
+    can_store_result = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["num_heads"])
+        self.n_kv_heads = int(p["num_kv_heads"])
+        self.key_dim = int(p["key_dim"])
+        self.values = p.get("values", "projected")
+        if self.values not in ("projected", "keys"):
+            raise ConfigError(f"softmax attention: values '{self.values}' (projected or keys)")
+        self.value_dim = int(p.get("value_dim") or self.key_dim)
+        if self.values == "keys" and self.value_dim != self.key_dim:
+            raise ConfigError(f"softmax attention: values that are the keys have the keys' width {self.key_dim}, "
+                              f"not {self.value_dim}")
+        self.scale = float(p["scale"])
+        self.softcap = float(p["softcap"]) if p.get("softcap") else None
+        self.slope_exponent = float(p["slope_exponent"]) if p.get("slope_exponent") else None
+        self.qk_norm_eps = float(p["qk_norm_eps"]) if p.get("qk_norm_eps") else 0.0
+        self.window: Optional[int] = int(p["window"]) if p.get("window") else None
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.output_gate = bool(p.get("output_gate", False))
+        self.names = dict(p.get("names", {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o"}))
+        kernels.check_row_widths(self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim)
+        self.position = make_part(p["position"]) if p.get("position") is not None else None
+        if self.position is not None:
+            if getattr(self.position, "layout", None) != "halves":
+                raise ConfigError("softmax attention rotates in the 'halves' layout (a rotary_tables part)")
+            if self.position.rotary_dim > self.key_dim:
+                raise ConfigError(f"softmax attention: {self.position.rotary_dim} rotated entries in heads of {self.key_dim}")
+            if self.qk_norm_eps:
+                raise ConfigError("softmax attention: either a rotation or unit-size q and k, not both")
+        self.q_width = self.n_heads * self.key_dim
+        self.k_width = self.n_kv_heads * self.key_dim
+        self.v_width = self.n_kv_heads * self.value_dim if self.values == "projected" else 0
+        self.o_width = self.n_heads * self.value_dim
+        self.w_in = self.w_o = self.slopes = None
+        self.window_chunk = 1
+
+    # ---- weights ----------------------------------------------------------
+    def _n(self, which: str) -> str:
+        return f"{self.prefix}{self.names[which]}"
+
+    def weight_specs(self):
+        specs = [WeightSpec(self._n("q"), (self.q_width, self.hidden), "matrix"),
+                 WeightSpec(self._n("k"), (self.k_width, self.hidden), "matrix")]
+        if self.values == "projected":
+            specs.append(WeightSpec(self._n("v"), (self.v_width, self.hidden), "matrix"))
+        if self.output_gate:
+            specs.append(WeightSpec(self._n("gate"), (self.o_width, self.hidden), "matrix"))
+        specs.append(WeightSpec(self._n("out"), (self.hidden, self.o_width), "matrix"))
+        return specs
+
+    def bind(self, tensors, runtime: Runtime, shared: Optional[dict] = None):
+        which = ["q", "k"] + (["v"] if self.values == "projected" else []) + (["gate"] if self.output_gate else [])
+        ws = [tensors[self._n(x)] for x in which]
+        if len({w.dtype for w in ws}) != 1:
+            ws = [w.to(torch.float32) for w in ws]
+        self.w_in = torch.cat(ws, dim=0).contiguous()        # one product: [q | k | (v) | (gate)]
+        self.w_o = tensors[self._n("out")].contiguous()
+        self.k_col = self.q_width
+        self.v_col = self.k_col + self.k_width if self.values == "projected" else -1
+        self.g_col = self.q_width + self.k_width + self.v_width
+        if self.slope_exponent is not None:
+            h = torch.arange(1, self.n_heads + 1, dtype=torch.float64)
+            self.slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64),
+                                    -self.slope_exponent * h / self.n_heads).to(torch.float32).to(runtime.device)
+        self.window_chunk = runtime.window_chunk
+        if self.position is not None:
+            self.position.bind(tensors, runtime, shared)
+            self.position.prepare(runtime, shared)
+
+    # ---- cache ------------------------------------------------------------
+    @property
+    def _ring(self) -> bool:
+        return self.window is not None and self.keep_first == 0
+
+    def cache_request(self):
+        return KVRequest(self.n_kv_heads, self.key_dim, self.window if self._ring else None,
+                         self.value_dim if self.value_dim != self.key_dim else None)
+
+    def _use_packed(self, start_pos, step_lens, owns_cache) -> bool:
+        """Prompts that start at position 0 and own their cache attend over the step's own keys."""
+        return owns_cache and all(s == 0 for s in start_pos) and any(n > 1 for n in step_lens)
+
+    def check_step(self, start_pos, step_lens, owns_cache):
+        if not self._ring or self._use_packed(start_pos, step_lens, owns_cache):
+            return
+        ring_tokens = ring_pages_for(self.window, self.window_chunk - 1) * PAGE_TOKENS
+        longest = max(step_lens)
+        if longest > ring_tokens - self.window + 1:
+            raise kernels.KernelError(
+                f"a layer with a window of {self.window} keeps {ring_tokens} keys per sequence and cannot continue "
+                f"a sequence by {longest} tokens in one step (at most {ring_tokens - self.window + 1}; the engine's "
+                f"window_chunk option sets this)")
+
+    # ---- one step -----------------------------------------------------------
+    def forward(self, x, ctx: StepContext, residual):
+        b, kv, dev = ctx.batch, ctx.kv, x.device
+        T = x.shape[0]
+        act = ctx.runtime.act_dtype
+        owns = kv is not None and kv.writes
+        packed = self._use_packed(b.host_start, b.host_lens, owns)
+        proj = kernels.linear(x, self.w_in, out_dtype=torch.float32)
+        kernels.mark("qkv")
+        q = torch.empty((T, self.q_width), dtype=act, device=dev)
+        k = torch.empty((T, self.k_width), dtype=act, device=dev) if packed else None
+        v = torch.empty((T, self.n_kv_heads * self.value_dim), dtype=act, device=dev) if packed else None
+        pos = self.position
+        kernels.head_encode(
+            proj, (b.tok_pos, b.tok_seq, b.new_lens), q, q_col=0, k_col=self.k_col, v_col=self.v_col,
+            n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
+            cos=pos.cos if pos is not None else None, sin=pos.sin if pos is not None else None,
+            rotary_dim=pos.rotary_dim if pos is not None else 0, norm_eps=self.qk_norm_eps, k_out=k, v_out=v,
+            k_pages=kv.k_pages if owns else None, v_pages=kv.v_pages if owns else None,
+            block_table=kv.block_table if owns else None, table_width=kv.table_width if owns else 0,
+            ring_pages=kv.ring_pages if owns else 0, page_tokens=kv.page_tokens if kv is not None else PAGE_TOKENS)
+        kernels.mark("rotary")
+        out = torch.empty((T, self.o_width), dtype=act, device=dev)
+        common = dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, key_dim=self.key_dim,
+                      value_dim=self.value_dim, tok_pos=b.tok_pos, tok_seq=b.tok_seq, cu_seqlens=b.cu_seqlens,
+                      start_pos=b.start_pos, scale=self.scale, window=self.window, keep_first=self.keep_first,
+                      softcap=self.softcap, slopes=self.slopes)
+        if packed:
+            kernels.attention_ext(q, out, k_packed=k, v_packed=v, **common)
+        else:
+            max_keys = b.max_new_len if self.window is None else min(b.max_new_len, self.window + self.keep_first)
+            n_splits = kernels.plan_splits(T, self.n_kv_heads, max_keys, ctx.runtime.sm_count)
+            scratch = None
+            if n_splits > 1:
+                scratch = torch.empty(kernels.split_scratch_floats(T, self.n_heads, self.value_dim, n_splits),
+                                      dtype=torch.float32, device=dev)
+            kernels.attention_ext(q, out, k_pages=kv.k_pages, v_pages=kv.v_pages, block_table=kv.block_table,
+                                  table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
+                                  n_splits=n_splits, scratch=scratch, **common)
+        if self.output_gate:
+            kernels.sigmoid_gate(out, proj[:, self.g_col:self.g_col + self.o_width])
+        kernels.mark("attention")
+        kernels.linear(out, self.w_o, out=residual, accumulate=not ctx.store_result)
+        kernels.mark("o")

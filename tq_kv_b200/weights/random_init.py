@@ -23,8 +23,11 @@ import torch
 
 from .safetensors_io import write_safetensors
 
-_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02, "norm_scale": 0.1, "norm_offset": 0.1, "conv": 0.3}
-_OFFSET = {"norm_scale": 1.0}
+_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02, "norm_scale": 0.1, "norm_offset": 0.1, "conv": 0.3,
+        "stream_read": 0.1, "stream_write": 0.1, "stream_mix": 0.1}
+_OFFSET = {"norm_scale": 1.0, "stream_write": 1.0}
+_HOST_MADE = ("stream_read", "stream_write", "stream_mix")      # a few numbers: made on the host for every device
+CHOICE_TABLE = "choice_table:"      # role "choice_table:<E>": int32 rows of distinct indices below E
 _MASK = (1 << 64) - 1
 _CHUNK = 1 << 15          # elements generated at a time on the host (stays in the cache)
 
@@ -115,9 +118,23 @@ def _host_tensor(key: int, n: int, std: float, offset: float) -> torch.Tensor:
     return torch.from_numpy(out)
 
 
+def _choice_table(key: int, shape: tuple[int, ...], n_choices: int) -> torch.Tensor:
+    """int32 [rows, top]: row r holds the `top` indices below n_choices whose draws (elements r * n_choices ..
+    of the tensor's stream) are the smallest, in that order: the entries of a row differ."""
+    rows, top = int(shape[0]), int(shape[1])
+    if top > n_choices:
+        raise ValueError(f"a row of {top} distinct indices below {n_choices} does not exist")
+    draws = np.concatenate([standard_normal_host(key, a, min(_CHUNK, rows * n_choices - a))
+                            for a in range(0, rows * n_choices, _CHUNK)]).reshape(rows, n_choices)
+    order = np.argsort(draws, axis=1, kind="stable")[:, :top]
+    return torch.from_numpy(order.astype(np.int32))
+
+
 def random_tensor(name: str, shape: tuple[int, ...], role: str, seed: int, dtype: torch.dtype, device) -> torch.Tensor:
     """The tensor `name` of the model seeded with `seed`, made on `device`
     (the same values on any device)."""
+    if role.startswith(CHOICE_TABLE):           # a small integer table: made on the host for every device
+        return _choice_table(tensor_key(seed, name), tuple(shape), int(role[len(CHOICE_TABLE):])).to(device)
     if role not in _STD:
         raise ValueError(f"no random-init rule for role '{role}' (tensor {name})")
     if any(int(d) < 0 for d in shape):
@@ -128,13 +145,18 @@ def random_tensor(name: str, shape: tuple[int, ...], role: str, seed: int, dtype
     for d in shape:
         n *= int(d)
     dev = torch.device(device)
-    if dev.type == "cuda":
+    if dev.type == "cuda" and role not in _HOST_MADE:
         from .. import kernels
         made = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
         t = torch.empty(shape, dtype=made, device=dev)
         kernels.random_fill(t, key, std, offset)
         return t if made == dtype else t.to(dtype)
-    return _host_tensor(key, n, std, offset).reshape(shape).to(dtype)
+    t = _host_tensor(key, n, std, offset).reshape(shape)
+    if role == "stream_read":                   # the sublayer reads about the streams' mean
+        t = t + 1.0 / float(shape[0])
+    elif role == "stream_mix":                  # the streams mostly keep to themselves
+        t = t + torch.eye(int(shape[0]))
+    return t.to(dtype).to(dev)
 
 
 def random_tensors(weight_specs, seed: int, dtype: torch.dtype, device) -> Iterator[tuple[str, torch.Tensor]]:
@@ -162,7 +184,8 @@ def write_model_folder(config_dict: dict, folder: str, seed: int, *, device="cpu
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(full, f, indent=1)
     write_safetensors(os.path.join(folder, "model.safetensors"),
-                      [(ws.name, dtype, tuple(ws.shape)) for ws in specs],
+                      [(ws.name, torch.int32 if ws.role.startswith(CHOICE_TABLE) else dtype, tuple(ws.shape))
+                       for ws in specs],
                       random_tensors(specs, seed, dtype, device),
                       metadata={"format": "pt", "seed": seed})
     return folder
