@@ -218,3 +218,11 @@ def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, la
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     cap = cfg.get("logit_softcap")
     return tanh_cap(logits, cap) if cap else logits
+
+
+def greedy(cfg: dict, weights: dict, prompt: list[int], n: int, dtype=torch.float64) -> list[int]:
+    """n greedy tokens after `prompt`, every step a whole forward pass (ties go to the lowest id)."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(decoder(cfg, weights, toks, dtype)[-1])))
+    return toks[len(prompt):]

@@ -48,8 +48,25 @@ __device__ __forceinline__ uint32_t fd_pack(float a, float b) {
 // table per head and distance; none: zero), nothing is normalised, so the warps' and the splits' partial outputs
 // simply add; with one split head h's output is multiplied by sigmoid(gate[token, h]) (none: one), with more the
 // kernel that adds the splits does that.
+// FD_SOFTMAX_EXT: the softmax with options (FdOptions): score * scale, capped by cap * tanh(. / cap), minus
+// slopes[h] * (i - j); behind a window the first keep_first keys stay in view.  The visible keys are counted
+// 0 .. n_keys-1: first the kept ones that the window has left behind, then the window's.
 #define FD_SOFTMAX 0
 #define FD_SIGMOID 1
+#define FD_SOFTMAX_EXT 2
+
+struct FdOptions {
+    float scale;            // natural units (the kernel's scale_log2 is this times log2 e)
+    float softcap;          // > 0: scores become softcap * tanh(score / softcap)
+    const float* slopes;    // [nh] or null
+    int keep_first;         // with a window: keys below this position stay visible
+};
+
+// cap * tanh(x / cap) with 2^x and the reciprocal of the special-function unit (a few ulp; tanh.approx is not enough)
+__device__ __forceinline__ float fd_tanh_cap(float x, float cap, float two_log2e_over_cap) {
+    const float t = exp2f(x * two_log2e_over_cap);       // e^(2x / cap); inf and 0 give +-cap
+    return cap * (1.f - __fdividef(2.f, t + 1.f));
+}
 
 // FD_CHUNK: keys per warp iteration — 16, or 32 for heads of up to 64 dims, whose 16-key chunks would be too small.
 // VT: 1 if the values have a tile of their own beside the keys' in every stage; 0 for a cache whose values are its
@@ -62,7 +79,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int window, float scale_log2,
                     bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv,
                     int n_splits, const float* __restrict__ bias = nullptr, int n_dist = 0,
-                    const float* __restrict__ gate = nullptr, int ldg = 0, int kv_div = 1) {
+                    const float* __restrict__ gate = nullptr, int ldg = 0, int kv_div = 1,
+                    FdOptions opt = FdOptions{0.f, 0.f, nullptr, 0}) {
     // kv_div > 1: more than 16 q heads share a key/value head; they are cut into kv_div groups, each a block row of
     // its own (nkv counts those groups), and group g reads the cache rows of head g / kv_div
     constexpr int ROW = HD * 2 + 16;                       // bytes per key row in shared memory (padded)
@@ -79,11 +97,17 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int pos = tok_pos[t];
     const int b = tok_seq[t];
     const int lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    int lo = lo_all, hi = pos + 1;
+    // the visible keys, counted 0 .. n_keys-1 (count c is position key_pos(c)): the kept first tokens that the
+    // window has left behind (none unless FD_SOFTMAX_EXT), then the window's keys lo_all .. pos
+    const int n_keep = (WEIGHTS == FD_SOFTMAX_EXT && opt.keep_first < lo_all) ? opt.keep_first
+                       : (WEIGHTS == FD_SOFTMAX_EXT ? lo_all : 0);
+    const int key_shift = lo_all - n_keep;
+    auto key_pos = [&](int c) { return c < n_keep ? c : c + key_shift; };
+    const int n_keys = n_keep + pos + 1 - lo_all;
+    int lo = 0, hi = n_keys;                               // [lo, hi): this block's keys, in that count
     if (n_splits > 1) {
-        const int keys = pos + 1 - lo_all;
-        const int split_len = (((keys + n_splits - 1) / n_splits) + 31) & ~31;
-        lo = lo_all + split * split_len;
+        const int split_len = (((n_keys + n_splits - 1) / n_splits) + 31) & ~31;
+        lo = split * split_len;
         if (lo + split_len < hi) hi = lo + split_len;
     }
     const int n_chunks = hi > lo ? (hi - lo + FD_CHUNK - 1) / FD_CHUNK : 0;
@@ -97,8 +121,9 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     auto issue = [&](int i) {
         const int chunk = warp + i * FD_WARPS;
         if (chunk < n_chunks) {
-            int j = lo + chunk * FD_CHUNK + (lane & (FD_CHUNK - 1));
-            if (j >= hi) j = hi - 1;                       // a valid address; the score is masked
+            int c = lo + chunk * FD_CHUNK + (lane & (FD_CHUNK - 1));
+            if (c >= hi) c = hi - 1;                       // a valid address; the score is masked
+            const int j = key_pos(c);
             int lp = j / FD_PAGE;
             if (ring_pages > 0) lp %= ring_pages;
             const unsigned long long my_row =
@@ -127,7 +152,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     // the predecessor; the positions and tables were copied in before the step's first kernel.  A block whose
     // keys are all older starts its copies before it waits.  (Were there earlier tokens of the same sequence
     // in this step, their keys would be new too: then the token is not its sequence's first row.)
-    const bool old_keys_only = hi <= pos && (t == 0 || tok_seq[t - 1] != b);
+    const bool old_keys_only = hi < n_keys && (t == 0 || tok_seq[t - 1] != b);
     if (old_keys_only) {
 #pragma unroll
         for (int i = 0; i < FD_STAGES - 1; ++i) issue(i);
@@ -196,6 +221,23 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         } else {
         // scale, mask keys beyond the range, online softmax (rows gid and gid + 8)
         float mx[2] = {-INFINITY, -INFINITY};
+        if constexpr (WEIGHTS == FD_SOFTMAX_EXT) {
+            const float sl0 = (opt.slopes && gid < n_rep) ? opt.slopes[g * n_rep + gid] : 0.f;
+            const float sl1 = (opt.slopes && gid + 8 < n_rep) ? opt.slopes[g * n_rep + gid + 8] : 0.f;
+            const float tc = opt.softcap > 0.f ? 2.f * 1.4426950408889634f / opt.softcap : 0.f;
+#pragma unroll
+            for (int nt = 0; nt < ST; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = j0 + nt * 8 + 2 * tid4 + (e & 1);
+                    float x = s[nt][e] * opt.scale;
+                    if (opt.softcap > 0.f) x = fd_tanh_cap(x, opt.softcap, tc);
+                    x = fmaf(-((e >> 1) ? sl1 : sl0), (float)(pos - key_pos(c)), x);
+                    const float v = c < hi ? x * 1.4426950408889634f : -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+        } else {
 #pragma unroll
         for (int nt = 0; nt < ST; ++nt)
 #pragma unroll
@@ -205,6 +247,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 s[nt][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -325,7 +368,8 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
                                int ring_pages, const int* tok_pos, const int* tok_seq, int window, float scale,
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
                                int pdl_family, cudaStream_t stream, const float* bias = nullptr, int n_dist = 0,
-                               const float* gate = nullptr, int ldg = 0, int kv_div = 1) {
+                               const float* gate = nullptr, int ldg = 0, int kv_div = 1,
+                               FdOptions opt = FdOptions{0.f, 0.f, nullptr, 0}) {
     constexpr int ROW = HD * 2 + 16;
     constexpr int FD_CHUNK = (HD <= 64 || !VT) ? 32 : 16;
     constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * (VT ? 2 : 1) * FD_CHUNK * ROW;
@@ -344,7 +388,7 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
     const dim3 grid(n_tokens, nkv, n_splits);
     return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK, WEIGHTS, VT>, grid, dim3(FD_WARPS * 32), smem, stream, q,
                          kp, vp, table, table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out,
-                         part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg, kv_div);
+                         part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg, kv_div, opt);
 }
 
 // Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach
@@ -414,6 +458,41 @@ TQ_API int tq_sigmoid_flash_decode(const void* q, const void* k_pages, const voi
                                                   block_table, table_width, 0, tok_pos, tok_seq, 0, scale, (bf16*)out, \
                                                   part, nullptr, n_tokens, nh, nkv, n_splits, TQ_PDL_FLASH_DECODE,      \
                                                   stream, bias, n_dist, gate, ldg)
+    switch (hd) {
+        TQ_FD(32);
+        TQ_FD(64);
+        TQ_FD(96);
+        TQ_FD(128);
+        default: return (int)cudaErrorNotSupported;
+    }
+#undef TQ_FD
+}
+
+
+// The softmax kernel with options (FD_SOFTMAX_EXT above): keys and values of one width.  Kept first tokens need a
+// cache that keeps all keys (no ring).  Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach.
+TQ_API int tq_flash_decode_ext(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                               int table_width, int ring_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
+                               int window, float scale, float softcap, const float* slopes, int keep_first, void* out,
+                               float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int hd, int n_splits,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || page_tokens != FD_PAGE) return (int)cudaErrorNotSupported;
+    if (keep_first < 0 || (keep_first > 0 && ring_pages > 0)) return (int)cudaErrorInvalidValue;
+    int kv_div = 1;
+    while (kv_div <= 64 && ((nh / nkv) % kv_div || nh / nkv / kv_div > 16)) ++kv_div;
+    if (kv_div > 64) return (int)cudaErrorNotSupported;
+    nkv *= kv_div;
+    if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorNotSupported;
+    if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
+    const FdOptions opt{scale, softcap, slopes, window > 0 ? keep_first : 0};
+#define TQ_FD(H)                                                                                                        \
+    case H:                                                                                                             \
+        return launch_flash_decode<H, FD_SOFTMAX_EXT>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages,      \
+                                                      block_table, table_width, ring_pages, tok_pos, tok_seq, window,   \
+                                                      scale, (bf16*)out, part_acc, part_ml, n_tokens, nh, nkv,          \
+                                                      n_splits, TQ_PDL_FLASH_DECODE, stream, nullptr, 0, nullptr, 0,    \
+                                                      kv_div, opt)
     switch (hd) {
         TQ_FD(32);
         TQ_FD(64);

@@ -54,11 +54,29 @@ struct FpSource {
     int page_tokens;
 };
 
-template <int HD>
+// Options of the EXT form of the kernel: score * scale, capped by softcap * tanh(. / softcap), minus
+// slopes[h] * (query position - key position); behind a window the first keep_first keys stay in view (their
+// tiles are walked first, then the window's); the result times sigmoid(gate[token, h * HD + d]) entry by entry.
+struct FpOptions {
+    float scale;            // natural units
+    float softcap;          // > 0: capped scores
+    const float* slopes;    // [nh] or null
+    int keep_first;
+    const float* gate;      // float32 logits [T, ldg] (column h * HD + d) or null
+    int ldg;
+};
+
+// cap * tanh(x / cap) with 2^x and a fast division (a few ulp; tanh.approx is not enough)
+__device__ __forceinline__ float fp_tanh_cap(float x, float cap, float two_log2e_over_cap) {
+    const float t = exp2f(x * two_log2e_over_cap);       // e^(2x / cap); inf and 0 give +-cap
+    return cap * (1.f - __fdividef(2.f, t + 1.f));
+}
+
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(FP_WARPS * 32)
 flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __restrict__ cu_seqlens,
                      const int* __restrict__ start_pos, int n_seqs, int window, float scale_log2,
-                     bf16* __restrict__ out, int nh, int nkv) {
+                     bf16* __restrict__ out, int nh, int nkv, FpOptions opt) {
     constexpr int ROW = HD * 2 + 16;                 // padded row: ldmatrix without bank conflicts
     constexpr int TILE = FP_BN * ROW;
     constexpr int KS = HD / 16;
@@ -92,7 +110,11 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
     const int p_last = start + min(len, tile * FP_BM + FP_BM) - 1;
     int j_begin = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
     j_begin &= ~(FP_BN - 1);
-    const int n_tiles = (p_last - j_begin) / FP_BN + 1;
+    // kept first tokens that lie in tiles before the window's first: those tiles come first
+    const int keep = (EXT && window > 0) ? opt.keep_first : 0;
+    const int keep_tiles = EXT ? min((keep + FP_BN - 1) / FP_BN, j_begin / FP_BN) : 0;
+    const int n_tiles = (p_last - j_begin) / FP_BN + 1 + keep_tiles;
+    auto tile_j0 = [&](int it) { return it < keep_tiles ? it * FP_BN : j_begin + (it - keep_tiles) * FP_BN; };
     const int packed_base = src.k_packed ? tok0 - start : 0;     // key j lives at packed token packed_base + j
 
     // Q fragments straight from global memory
@@ -114,7 +136,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
     auto load_tile = [&](int it) {
         unsigned char* ks_ = smem + (it & 1) * 2 * TILE;
         unsigned char* vs_ = ks_ + TILE;
-        const int j0 = j_begin + it * FP_BN;
+        const int j0 = tile_j0(it);
         for (int p = threadIdx.x; p < FP_BN * PR; p += FP_WARPS * 32) {
             const int key = p / PR, c = p - key * PR;
             int j = j0 + key;
@@ -148,7 +170,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
         __syncthreads();
         const unsigned char* ks_ = smem + (it & 1) * 2 * TILE;
         const unsigned char* vs_ = ks_ + TILE;
-        const int j0 = j_begin + it * FP_BN;
+        const int j0 = tile_j0(it);
 
         float s[FP_BN / 8][4];
 #pragma unroll
@@ -168,7 +190,24 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
         // wholly inside every row's range (the same answer for the whole block): they skip the tests.
         float mx[2] = {-INFINITY, -INFINITY};
         const bool inside = j0 + FP_BN - 1 <= p_first && (window <= 0 || j0 > p_last - window);
-        if (inside) {
+        if constexpr (EXT) {
+            const float slope = opt.slopes ? opt.slopes[h] : 0.f;
+            const float tc = opt.softcap > 0.f ? 2.f * 1.4426950408889634f / opt.softcap : 0.f;
+#pragma unroll
+            for (int n = 0; n < FP_BN / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + n * 8 + 2 * tid4 + (e & 1);
+                    const int p = rp[e >> 1];
+                    const bool seen = inside || (j <= p && (window <= 0 || j > p - window || j < keep));
+                    float x = s[n][e] * opt.scale;
+                    if (opt.softcap > 0.f) x = fp_tanh_cap(x, opt.softcap, tc);
+                    x = fmaf(-slope, (float)(p - j), x);
+                    const float v = seen ? x * 1.4426950408889634f : -INFINITY;
+                    s[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+        } else if (inside) {
 #pragma unroll
             for (int n = 0; n < FP_BN / 8; ++n)
 #pragma unroll
@@ -243,31 +282,36 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
         if (ri[r] >= len) continue;
         const float inv = 1.f / l_run[r];
         bf16* orow = out + ((size_t)(tok0 + ri[r]) * nh + h) * HD;
+        const float* grow = (EXT && opt.gate) ? opt.gate + (size_t)(tok0 + ri[r]) * opt.ldg + (size_t)h * HD : nullptr;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
             const int d = n * 8 + 2 * tid4;
-            *reinterpret_cast<__nv_bfloat162*>(orow + d) =
-                __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+            float a = o[n][2 * r] * inv, c = o[n][2 * r + 1] * inv;
+            if (EXT && grow) {
+                a = __fdividef(a, 1.f + __expf(-grow[d]));
+                c = __fdividef(c, 1.f + __expf(-grow[d + 1]));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(orow + d) = __floats2bfloat162_rn(a, c);
         }
     }
 }
 
-template <int HD>
+template <int HD, bool EXT = false>
 static int launch_flash_prefill(const bf16* q, const FpSource& src, const int* cu_seqlens, const int* start_pos,
                                 int n_seqs, int n_tokens, int window, float scale, bf16* out, int nh, int nkv,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, FpOptions opt = FpOptions{0.f, 0.f, nullptr, 0, nullptr, 0}) {
     constexpr size_t smem = 2 * 2 * FP_BN * (HD * 2 + 16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     // an upper bound on the number of 64-token tiles: every sequence may add one partial tile
     const dim3 grid((n_tokens + FP_BM - 1) / FP_BM + n_seqs, nh);
-    flash_prefill_kernel<HD><<<grid, FP_WARPS * 32, smem, stream>>>(q, src, cu_seqlens, start_pos, n_seqs, window,
-                                                                   scale * 1.4426950408889634f, out, nh, nkv);
+    flash_prefill_kernel<HD, EXT><<<grid, FP_WARPS * 32, smem, stream>>>(q, src, cu_seqlens, start_pos, n_seqs, window,
+                                                                        scale * 1.4426950408889634f, out, nh, nkv, opt);
     return tq_launch_status();
 }
 
@@ -286,6 +330,35 @@ TQ_API int tq_flash_prefill(const void* q, const void* k_packed, const void* v_p
     case H:                                                                                                   \
         return launch_flash_prefill<H>((const bf16*)q, src, cu_seqlens, start_pos, n_seqs, n_tokens, window, \
                                        scale, (bf16*)out, nh, nkv, stream)
+    switch (hd) {
+        TQ_FP(32);
+        TQ_FP(64);
+        TQ_FP(96);
+        TQ_FP(128);
+        default: return (int)cudaErrorNotSupported;
+    }
+#undef TQ_FP
+}
+
+
+// The same kernel with options (FpOptions above): keys and values of one width.  Kept first tokens need a cache
+// that keeps all keys (no ring).  Returns cudaErrorNotSupported (801) for head sizes outside {32, 64, 96, 128}.
+TQ_API int tq_flash_prefill_ext(const void* q, const void* k_packed, const void* v_packed, const void* k_pages,
+                                const void* v_pages, const int* block_table, int table_width, int ring_pages,
+                                int page_tokens, const int* cu_seqlens, const int* start_pos, int n_seqs, int n_tokens,
+                                int window, float scale, float softcap, const float* slopes, int keep_first,
+                                const float* gate, int ldg, void* out, int nh, int nkv, int hd, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh > 65535) return (int)cudaErrorNotSupported;
+    if (!k_packed && (!k_pages || !block_table || page_tokens <= 0)) return (int)cudaErrorInvalidValue;
+    if (keep_first < 0 || (keep_first > 0 && !k_packed && ring_pages > 0)) return (int)cudaErrorInvalidValue;
+    FpSource src{(const bf16*)k_packed, (const bf16*)v_packed, (const bf16*)k_pages, (const bf16*)v_pages,
+                 block_table, table_width, ring_pages, page_tokens};
+    const FpOptions opt{scale, softcap, slopes, keep_first, gate, ldg};
+#define TQ_FP(H)                                                                                                    \
+    case H:                                                                                                         \
+        return launch_flash_prefill<H, true>((const bf16*)q, src, cu_seqlens, start_pos, n_seqs, n_tokens, window, \
+                                             scale, (bf16*)out, nh, nkv, stream, opt)
     switch (hd) {
         TQ_FP(32);
         TQ_FP(64);

@@ -158,8 +158,22 @@ __device__ __forceinline__ uint64_t ft_desc_mn(uint32_t saddr, uint32_t mn_strid
 // multiplies head h's row by sigmoid(gate[token, h]) (none: one).  The weights are made in float32 (2^x and the
 // reciprocal of the special-function unit, a few ulp) and rounded to bfloat16 for the second product, as the
 // softmax's are.
+// FT_SOFTMAX_EXT: the softmax with options (FtOptions): score * scale, capped by softcap * tanh(. / softcap), minus
+// slopes[h] * (query position - key position); behind a window the first keep_first keys stay in view (the tiles
+// that hold them are walked first, then the window's); the result times sigmoid(gate[token, h * HD + d]) entry by
+// entry.  The scores are transformed in float32 before the maximum is taken.
 #define FT_SOFTMAX 0
 #define FT_SIGMOID 1
+#define FT_SOFTMAX_EXT 2
+
+struct FtOptions {
+    float scale;            // natural units
+    float softcap;          // > 0: capped scores
+    const float* slopes;    // [nh] or null
+    int keep_first;
+    const float* gate;      // float32 logits [T, ldg] (column h * HD + d) or null
+    int ldg;
+};
 
 template <int HD, bool PAGED, int WEIGHTS>
 __global__ void __launch_bounds__(FT_THREADS, 2)
@@ -168,7 +182,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         int ring_pages, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
                         int n_seqs, int window, float scale_log2, bf16* __restrict__ out, int nh, int nkv,
                         int* __restrict__ status, const float* __restrict__ bias, int n_dist,
-                        const float* __restrict__ gate, int ldg) {
+                        const float* __restrict__ gate, int ldg, FtOptions opt) {
     constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of a Q, K or V tile
     constexpr int Q_BYTES = SUBS * FT_SUB_BYTES;
     constexpr int KV_BYTES = SUBS * FT_KV_SUB_BYTES;       // a K or V tile of 64 keys
@@ -214,7 +228,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int p_last = start + min(len, tile * FT_BM + FT_BM) - 1;
     int j_begin = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
     j_begin &= ~(FT_BN - 1);
-    const int n_tiles = (p_last - j_begin) / FT_BN + 1;
+    // kept first tokens that lie in tiles before the window's first: those tiles come first
+    const int keep = (WEIGHTS == FT_SOFTMAX_EXT && window > 0) ? opt.keep_first : 0;
+    const int keep_tiles = WEIGHTS == FT_SOFTMAX_EXT ? min((keep + FT_BN - 1) / FT_BN, j_begin / FT_BN) : 0;
+    const int n_tiles = (p_last - j_begin) / FT_BN + 1 + keep_tiles;
+    auto tile_j0 = [&](int it) { return it < keep_tiles ? it * FT_BN : j_begin + (it - keep_tiles) * FT_BN; };
 
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ft_smem(q_full)));
@@ -255,7 +273,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 ft_tma(ft_smem(q_s + sub * FT_SUB_BYTES), &map_q, h * HD + sub * 64, tok0 + tile * FT_BM, ft_smem(q_full));
             for (int it = 0; it < n_tiles; ++it) {
                 const int s = it & 1;
-                const int j0 = j_begin + it * FT_BN;
+                const int j0 = tile_j0(it);
                 int row;
                 if (PAGED) {
                     int lp = j0 / 64;
@@ -336,7 +354,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles && ok; ++it) {
-            const int j0 = j_begin + it * FT_BN;
+            const int j0 = tile_j0(it);
             if (!ft_wait(ft_smem(&s_full[it & 1]), (it >> 1) & 1, true)) { *failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t s_addr = tmem_s + (it & 1) * FT_BN + lane_addr;
@@ -352,6 +370,25 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 for (int j = 0; j < FT_BN; ++j) {
                     const int key = j0 + j;
                     if (key < j_lo || key > j_hi) sv[j] = -INFINITY;     // a masked key: 2^-inf = 0 below
+                }
+            }
+            if constexpr (WEIGHTS == FT_SOFTMAX_EXT) {
+                // the scores in units of log2: (cap(score * scale) - slope * distance) * log2 e; masked: -inf
+                const float slope = opt.slopes ? opt.slopes[h] : 0.f;
+                const float tc = opt.softcap > 0.f ? 2.f * 1.4426950408889634f / opt.softcap : 0.f;
+                const bool capped = opt.softcap > 0.f;
+#pragma unroll
+                for (int j = 0; j < FT_BN; ++j) {
+                    const int key = j0 + j;
+                    float x = sv[j] * opt.scale;
+                    if (capped) {
+                        float r;
+                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(ft_exp2(x * tc) + 1.f));
+                        x = opt.softcap * fmaf(-2.f, r, 1.f);
+                    }
+                    x = fmaf(-slope, (float)(p_row - key), x) * 1.4426950408889634f;
+                    const bool seen = inside || (key <= j_hi && (key >= j_lo || key < keep));
+                    sv[j] = seen ? x : -INFINITY;
                 }
             }
             if constexpr (WEIGHTS == FT_SIGMOID) {
@@ -389,7 +426,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 mx4[3] = fmaxf(mx4[3], sv[j + 3]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_tile = mx * scale_log2;
+            const float sl = WEIGHTS == FT_SOFTMAX_EXT ? 1.f : scale_log2;      // EXT: already in units of log2
+            const float m_tile = mx * sl;
             const bool grow = m_tile > m_ref + 8.f;          // also true for the first finite maximum
             if (__any_sync(0xffffffffu, grow) && it > 0) {
                 // O is in use until the P·V of the tile before is done
@@ -418,8 +456,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             float packed[FT_BN / 2];
 #pragma unroll
             for (int j = 0; j < FT_BN; j += 2) {
-                const float p0 = ft_exp2(fmaf(sv[j], scale_log2, neg_ref));
-                const float p1 = ft_exp2(fmaf(sv[j + 1], scale_log2, neg_ref));
+                const float p0 = ft_exp2(fmaf(sv[j], sl, neg_ref));
+                const float p1 = ft_exp2(fmaf(sv[j + 1], sl, neg_ref));
                 rs4[(j >> 1) & 3] += p0 + p1;
                 __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                 packed[j >> 1] = __uint_as_float(*reinterpret_cast<uint32_t*>(&pk));
@@ -443,10 +481,22 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if constexpr (WEIGHTS == FT_SIGMOID)
                 inv = gate ? 1.f / (1.f + expf(-gate[(size_t)(tok0 + min(i_row, len - 1)) * ldg + h])) : 1.f;
             bf16* orow = out + ((size_t)(tok0 + min(i_row, len - 1)) * nh + h) * HD;
+            const float* grow = (WEIGHTS == FT_SOFTMAX_EXT && opt.gate)
+                                    ? opt.gate + (size_t)(tok0 + min(i_row, len - 1)) * opt.ldg + (size_t)h * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
                 float v[32];
                 ft_ld32(tmem_o + lane_addr + c, v);           // (all lanes take part in the load)
+                if (WEIGHTS == FT_SOFTMAX_EXT && grow) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4) {
+                        const float4 gv = *reinterpret_cast<const float4*>(grow + c + d);
+                        v[d] = __fdividef(v[d], 1.f + __expf(-gv.x));
+                        v[d + 1] = __fdividef(v[d + 1], 1.f + __expf(-gv.y));
+                        v[d + 2] = __fdividef(v[d + 2], 1.f + __expf(-gv.z));
+                        v[d + 3] = __fdividef(v[d + 3], 1.f + __expf(-gv.w));
+                    }
+                }
                 if (i_row < len) {
 #pragma unroll
                     for (int d = 0; d < 32; d += 8) {
@@ -487,7 +537,7 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      int table_width, int ring_pages, const int* cu_seqlens, const int* start_pos, int n_seqs,
                      int n_tokens, int window, float scale, bf16* out, int nh, int nkv, int* status,
                      cudaStream_t stream, const float* bias = nullptr, int n_dist = 0, const float* gate = nullptr,
-                     int ldg = 0) {
+                     int ldg = 0, FtOptions opt = FtOptions{0.f, 0.f, nullptr, 0, nullptr, 0}) {
     constexpr int SMEM = (HD / 64) * (FT_SUB_BYTES + 4 * FT_KV_SUB_BYTES) + 256;
     static bool configured = false;
     if (!configured) {
@@ -499,7 +549,7 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     const dim3 grid(nh, (n_tokens + FT_BM - 1) / FT_BM + n_seqs);
     return tq_launch_pdl(TQ_PDL_PREFILL_ATTENTION, flash_prefill_tc_kernel<HD, PAGED, WEIGHTS>, grid, dim3(FT_THREADS), SMEM,
                          stream, mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
-                         scale * 1.4426950408889634f, out, nh, nkv, status, bias, n_dist, gate, ldg);
+                         scale * 1.4426950408889634f, out, nh, nkv, status, bias, n_dist, gate, ldg, opt);
 }
 
 // q, out [T, nh * hd] bfloat16.  Keys/values: packed [T, nkv * hd] (every
@@ -564,6 +614,45 @@ TQ_API int tq_sigmoid_prefill_tc(const void* q, const void* k_packed, const void
 #define TQ_FT(H, P) return ft_launch<H, P, FT_SIGMOID>(mq, mk, mv, block_table, table_width, 0, cu_seqlens, start_pos, \
                                                        n_seqs, n_tokens, 0, scale, (bf16*)out, nh, nkv, status, stream, \
                                                        bias, n_dist, gate, ldg)
+    if (hd == 128 && paged) TQ_FT(128, true);
+    if (hd == 128 && !paged) TQ_FT(128, false);
+    if (hd == 64 && paged) TQ_FT(64, true);
+    TQ_FT(64, false);
+#undef TQ_FT
+}
+
+
+// The softmax kernel with options (FT_SOFTMAX_EXT above): keys and values of one width (64 or 128).  Kept first
+// tokens need a cache that keeps all keys (no ring).  gate: float32 logits, one per token and output entry (row
+// stride ldg, a multiple of 4, 16-byte aligned), or null.
+TQ_API int tq_flash_prefill_tc_ext(const void* q, const void* k_packed, const void* v_packed, const void* k_pages,
+                                   const void* v_pages, long long n_pages, const int* block_table, int table_width,
+                                   int ring_pages, int page_tokens, const int* cu_seqlens, const int* start_pos,
+                                   int n_seqs, int n_tokens, int window, float scale, float softcap,
+                                   const float* slopes, int keep_first, const float* gate, int ldg, void* out, int nh,
+                                   int nkv, int hd, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || (hd != 64 && hd != 128)) return (int)cudaErrorNotSupported;
+    if ((long long)(n_tokens + FT_BM - 1) / FT_BM + n_seqs > 65535) return (int)cudaErrorNotSupported;   // grid.y
+    const bool paged = k_packed == nullptr;
+    if (paged && (page_tokens != 64 || !k_pages || !v_pages || !block_table)) return (int)cudaErrorNotSupported;
+    if (keep_first < 0 || (keep_first > 0 && paged && ring_pages > 0)) return (int)cudaErrorInvalidValue;
+    if (gate && ((ldg & 3) || (reinterpret_cast<uintptr_t>(gate) & 15))) return (int)cudaErrorNotSupported;
+    CUtensorMap mq, mk, mv;
+    int st = ft_map(&mq, q, (uint64_t)n_tokens, (uint64_t)nh * hd, (uint64_t)nh * hd, FT_BM);
+    if (st) return st;
+    if (paged) {
+        st = ft_map(&mk, k_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+        if (!st) st = ft_map(&mv, v_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+    } else {
+        st = ft_map(&mk, k_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+        if (!st) st = ft_map(&mv, v_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+    }
+    if (st) return st;
+    const FtOptions opt{scale, softcap, slopes, keep_first, gate, ldg};
+#define TQ_FT(H, P) return ft_launch<H, P, FT_SOFTMAX_EXT>(mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, \
+                                                           start_pos, n_seqs, n_tokens, window, scale, (bf16*)out, nh,    \
+                                                           nkv, status, stream, nullptr, 0, nullptr, 0, opt)
     if (hd == 128 && paged) TQ_FT(128, true);
     if (hd == 128 && !paged) TQ_FT(128, false);
     if (hd == 64 && paged) TQ_FT(64, true);

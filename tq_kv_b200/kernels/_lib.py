@@ -216,6 +216,15 @@ _SIGNATURES = {
     "tq_attention_ext": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
                          c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
+    "tq_flash_prefill_tc_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int,
+                                c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                                c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tq_flash_prefill_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p,
+                             c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tq_flash_decode_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                            c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int, c_int, c_void_p],
     "tq_head_encode": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],

@@ -134,14 +134,20 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
                   k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                   block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
                   page_tokens: int = 64, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                  use_fast: bool = True):
+                  gate: Optional[torch.Tensor] = None, use_fast: bool = True):
     """Softmax attention with options: for the query at position i of head h and the key at position j <= i,
 
         s = q . k * scale;   s <- softcap * tanh(s / softcap)  (if a cap is given);
         s <- s - slopes[h] * (i - j)                            (if slopes are given);
 
     j is visible if i - j < window or j < keep_first (no window: every j <= i).  Value rows may have another
-    width than the keys.  q [T, nh*key_dim], out [T, nh*value_dim]; keys and values as in `attention`."""
+    width than the keys.  q [T, nh*key_dim], out [T, nh*value_dim]; keys and values as in `attention`.
+    `gate` (float32 [T, nh*value_dim], possibly a column slice of wider rows): out *= sigmoid(gate), in the
+    attention kernel's last step where it can, else by a kernel of its own.
+
+    bfloat16 with keys and values of one width runs on the tensor cores: prompts on the tcgen05 kernel (heads of
+    64 and 128) or the mma.sync one (32, 64, 96, 128), single tokens on the bandwidth-built cache kernel; all
+    else, and float32, on the general kernel."""
     check_row_widths(n_heads, n_kv_heads, key_dim, value_dim)
     T = q.shape[0]
     if q.shape[1] != n_heads * key_dim or tuple(out.shape) != (T, n_heads * value_dim) or out.dtype != q.dtype:
@@ -170,10 +176,59 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
         part_acc, part_ml = scratch[:n_acc], scratch[n_acc:need]
     need_contiguous(q=q, out=out, k_packed=k_packed, v_packed=v_packed, k_pages=k_pages, v_pages=v_pages,
                     block_table=block_table, slopes=slopes)
+    if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != tuple(out.shape)
+                             or gate.stride(1) != 1):
+        raise KernelError("attention: the gate must be float32 of the result's shape")
+    keep = int(keep_first) if window else 0
+    n_seqs = cu_seqlens.shape[0] - 1
+    fast = use_fast and q.dtype == torch.bfloat16 and key_dim == value_dim
+    if fast and T > n_seqs:                                  # prompts (some sequence brings several tokens)
+        gate_ok = gate is not None and gate.stride(0) % 4 == 0 and gate.data_ptr() % 16 == 0
+        g_ptr, g_ld = (ptr(gate), gate.stride(0)) if gate_ok else (None, 0)
+        st = NOT_SUPPORTED
+        if USE_TC_ATTENTION:
+            st = core().tq_flash_prefill_tc_ext(
+                ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages),
+                0 if k_pages is None else k_pages.shape[0], ptr(block_table), table_width, ring_pages, page_tokens,
+                ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale), float(softcap or 0.0),
+                ptr(slopes), keep, g_ptr, g_ld, ptr(out), n_heads, n_kv_heads, key_dim,
+                ptr(tc_status_word(q.device)), stream())
+            if st != NOT_SUPPORTED:
+                check(st, "flash_prefill_tc_ext")
+        if st == NOT_SUPPORTED:
+            st = core().tq_flash_prefill_ext(
+                ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width,
+                ring_pages, page_tokens, ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale),
+                float(softcap or 0.0), ptr(slopes), keep, g_ptr, g_ld, ptr(out), n_heads, n_kv_heads, key_dim,
+                stream())
+            if st != NOT_SUPPORTED:
+                check(st, "flash_prefill_ext")
+        if st != NOT_SUPPORTED:
+            if gate is not None and not gate_ok:
+                from .elementwise import sigmoid_gate
+                sigmoid_gate(out, gate)
+            return out
+    if fast and not packed:
+        st = core().tq_flash_decode_ext(
+            ptr(q), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width, ring_pages, page_tokens, ptr(tok_pos),
+            ptr(tok_seq), int(window or 0), float(scale), float(softcap or 0.0), ptr(slopes), keep, ptr(out),
+            ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim, n_splits, stream())
+        if st != NOT_SUPPORTED:
+            check(st, "flash_decode_ext")
+            if n_splits > 1:
+                check(core().tq_attention_merge(ptr(part_acc), ptr(part_ml), ptr(out), dtype_code(out), T, n_heads,
+                                                value_dim, n_splits, stream()), "attention_merge")
+            if gate is not None:
+                from .elementwise import sigmoid_gate
+                sigmoid_gate(out, gate)
+            return out
     check(core().tq_attention_ext(
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
         table_width, ring_pages, page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos),
         int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim,
-        value_dim, float(softcap or 0.0), ptr(slopes), int(keep_first) if window else 0, n_splits, stream()),
+        value_dim, float(softcap or 0.0), ptr(slopes), keep, n_splits, stream()),
         "attention_ext", 2 if n_splits > 1 else 1)
+    if gate is not None:
+        from .elementwise import sigmoid_gate
+        sigmoid_gate(out, gate)
     return out

@@ -23,7 +23,9 @@ kernel encodes q and k, splits the heads and appends k and v to the cache
 (csrc/head_encode.cu).  Prompts from position 0 attend over the step's own keys;
 everything else reads the paged cache: a ring for a plain window, all keys where
 first tokens are kept (the kernels skip what lies between the kept tokens and the
-window).  Scores, softmax and the bias are float32.
+window).  Scores, softmax and the bias are float32.  bfloat16 steps whose keys and
+values have one width run the tensor-core kernels (`kernels.attention_ext`), which
+also apply the output gate where they can.
 """
 from __future__ import annotations
 
@@ -163,7 +165,8 @@ class SoftmaxAttention(Mixer):
         common = dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, key_dim=self.key_dim,
                       value_dim=self.value_dim, tok_pos=b.tok_pos, tok_seq=b.tok_seq, cu_seqlens=b.cu_seqlens,
                       start_pos=b.start_pos, scale=self.scale, window=self.window, keep_first=self.keep_first,
-                      softcap=self.softcap, slopes=self.slopes)
+                      softcap=self.softcap, slopes=self.slopes,
+                      gate=proj[:, self.g_col:self.g_col + self.o_width] if self.output_gate else None)
         if packed:
             kernels.attention_ext(q, out, k_packed=k, v_packed=v, **common)
         else:
@@ -176,8 +179,6 @@ class SoftmaxAttention(Mixer):
             kernels.attention_ext(q, out, k_pages=kv.k_pages, v_pages=kv.v_pages, block_table=kv.block_table,
                                   table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
                                   n_splits=n_splits, scratch=scratch, **common)
-        if self.output_gate:
-            kernels.sigmoid_gate(out, proj[:, self.g_col:self.g_col + self.o_width])
         kernels.mark("attention")
         kernels.linear(out, self.w_o, out=residual, accumulate=not ctx.store_result)
         kernels.mark("o")
