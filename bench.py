@@ -26,11 +26,11 @@ then 256 decode steps.  Peaks come from MEASURED_PEAKS.json beside this file
 if it exists, else from an earlier measurement on the same kind of machine
 (6.65 TB/s, 1.59 PFLOP/s).
 
-`--design zodosun|rirudra [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the named decoder beside the Qwen2
+`--design zodosun|rirudra|pavisun [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the named decoder beside the Qwen2
 decoder of the same width, depth, heads, feed-forward and vocabulary (random weights, bfloat16): device time of a
 prompt, of decode steps at batch 8 and 64, and the time by class of kernel with what the attention and scan
 kernels reach of their rooflines, as one JSON line of its own (`--design rirudra` also runs the Zodosun decoder,
-whose scans are the like kernels of its own).  The default workload and its line are untouched.
+whose scans are the like kernels of its own; `--design pavisun` runs the Pavisun decoder and the Qwen2 decoder only).  The default workload and its line are untouched.
 
 The reference arm (`--impl reference`) cannot run here: the reference is a
 Rust workspace and no Rust toolchain is installed, so it prints its
@@ -229,6 +229,78 @@ def rirudra_config(width: int, ff: int, layers: int, vocab: int) -> dict:
             "layers": [order[i % 4] for i in range(layers)]}
 
 
+PAVISUN_WINDOW, PAVISUN_KEPT, PAVISUN_EXPERTS, PAVISUN_TOP, PAVISUN_STREAMS = 1024, 4, 8, 2, 4
+
+
+def pavisun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
+    """A Pavisun configuration of the given width: heads of 128 on a quarter as many key heads; layers alternate
+    between the mixer of unit-size q and k (distance slopes, a window of 1,024 that keeps the first 4 tokens, an
+    output gate) and the rotating mixer whose values are its keys (capped scores, a window of 1,024, rotation
+    stretched 8 times); 8 experts of half the feed-forward width of which a token uses 2 (as many products per
+    token as the dense feed-forward has); 4 residual streams; capped logits."""
+    heads, kv = width // 128, max(1, width // 512)
+    mlp = {"kind": "moe", "expert": {"ff": ff // PAVISUN_TOP}, "router": {"experts": PAVISUN_EXPERTS, "top": PAVISUN_TOP}}
+    unit = {"type": "attention_2", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 1.0,
+        "mask": {"size": PAVISUN_WINDOW, "keep_first": PAVISUN_KEPT}}}
+    rot = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+        "mask": {"size": PAVISUN_WINDOW},
+        "rot": {"base": 1e6, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Pavisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "streams": PAVISUN_STREAMS, "logit_softcap": 30.0, "max_positions": 8192,
+            "layers": [unit if i % 2 == 0 else rot for i in range(layers)]}
+
+
+def pavisun_roofline(rec: dict, pk: dict, P: int) -> dict:
+    """What the classes of the Pavisun decoder reach of their rooflines, beside the like classes of the Qwen2
+    decoder: attention (tensor throughput in a prompt, key and value bytes in decoding), the feed-forward (tensor
+    throughput in a prompt, weight bytes in decoding) and the kernels between the sublayers (bytes)."""
+    width, ff, layers = rec["width"], rec["ff"], rec["layers"]
+    heads, kv, d = width // 128, max(1, width // 512), 128
+    p, q = rec["pavisun"], rec["qwen2"]
+    n_unit = (layers + 1) // 2
+    n_rot = layers - n_unit
+    Wd, K, S, E, top = PAVISUN_WINDOW, PAVISUN_KEPT, PAVISUN_STREAMS, PAVISUN_EXPERTS, PAVISUN_TOP
+
+    def frac_tensor(flops, us):
+        return round(flops / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+
+    def frac_hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+
+    seen_win = sum(min(i + 1, Wd) for i in range(P))                    # keys a prompt's rows see in a window
+    seen_kept = seen_win + sum(min(K, max(0, i + 1 - Wd)) for i in range(P))
+    roof = {}
+    roof["pavisun.prefill.attention.frac_of_bf16"] = frac_tensor(
+        4 * heads * d * (seen_kept * n_unit + seen_win * n_rot), p["prefill_classes_us"]["attention"])
+    roof["qwen2.prefill.attention.frac_of_bf16"] = frac_tensor(
+        4 * heads * d * P * (P + 1) / 2 * layers, q["prefill_classes_us"]["attention"])
+    n_ff = layers
+    roof["pavisun.prefill.experts.frac_of_bf16"] = frac_tensor(
+        6 * P * top * width * (ff // top) * n_ff, p["prefill_classes_us"]["experts"])
+    roof["qwen2.prefill.feed_forward.frac_of_bf16"] = frac_tensor(
+        6 * P * width * ff * layers, q["prefill_classes_us"]["gate_up"] + q["prefill_classes_us"]["down"])
+    # between the sublayers: the streams are read and written once per sublayer (float32), the normed sum written
+    # (bfloat16) and the sublayer's result read (float32); the plain decoder reads and writes one residual row
+    between_p = P * width * (2 * S * 4 + 2 + 4) * 2 * layers
+    between_q = P * width * (2 * 2 + 2 + 2) * 2 * layers
+    roof["pavisun.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(between_p, p["prefill_classes_us"]["norms"])
+    roof["qwen2.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(between_q, q["prefill_classes_us"]["norms"])
+    # decoding, 64 sequences that hold P + 16 tokens: a row of keys is read once where the values are the keys
+    keys = min(P + 16, Wd)
+    row = kv * d * 2
+    roof["pavisun.decode_b64.attention.frac_of_hbm"] = frac_hbm(
+        64 * ((keys + K) * 2 * row * n_unit + keys * row * n_rot), p["decode_b64_classes_us"]["attention"])
+    roof["qwen2.decode_b64.attention.frac_of_hbm"] = frac_hbm(
+        64 * (P + 16) * 2 * row * layers, q["decode_b64_classes_us"]["attention"])
+    roof["pavisun.decode_b64.experts.frac_of_hbm"] = frac_hbm(
+        E * 3 * width * (ff // top) * 2 * n_ff, p["decode_b64_classes_us"]["experts"])
+    roof["qwen2.decode_b64.feed_forward.frac_of_hbm"] = frac_hbm(
+        3 * width * ff * 2 * layers, q["decode_b64_classes_us"]["gate_up"] + q["decode_b64_classes_us"]["down"])
+    return roof
+
+
 def rirudra_roofline(rec: dict, pk: dict, P: int, sms: int) -> dict:
     """What the attention and scan classes of the Rirudra decoder reach of their rooflines, beside the like classes
     of the Qwen2 decoder (attention) and of the Zodosun decoder (scans)."""
@@ -287,6 +359,8 @@ def design_compare(args) -> int:
             models = [("zodosun", zod), ("qwen2", qwen)]
             if args.design == "rirudra":
                 models.insert(0, ("rirudra", rirudra_config(width, ff, layers, vocab)))
+            if args.design == "pavisun":
+                models = [("pavisun", pavisun_config(width, ff, layers, vocab)), ("qwen2", qwen)]
             for model, cfg in models:
                 eng = tq.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=64, max_context=ctx,
                                             max_tokens=64 * ctx)
@@ -340,7 +414,8 @@ def design_compare(args) -> int:
                         eng.use_graphs = False
 
                         def one_step():
-                            eng.step([StepRow(s, [1], [0]) for s in slots], keep_logits=False)
+                            eng.step([StepRow(s, [(37 * j + 1) % vocab], [0]) for j, s in enumerate(slots)],
+                                     keep_logits=False)
 
                         one_step()
                         r["decode_b64_classes_us"] = {k: round(v, 1) for k, v in timed_by_class(one_step).items()
@@ -352,6 +427,9 @@ def design_compare(args) -> int:
                 torch.cuda.empty_cache()
             if args.design == "rirudra":
                 rec["roofline"] = rirudra_roofline(rec, pk, P, sms)
+                continue
+            if args.design == "pavisun":
+                rec["roofline"] = pavisun_roofline(rec, pk, P)
                 continue
             # what the classes reach of their rooflines
             heads, d = width // 128, 128
@@ -385,7 +463,7 @@ def design_compare(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zodosun", "rirudra"],
+    ap.add_argument("--design", default=None, choices=["zodosun", "rirudra", "pavisun"],
                     help="instead of the default workload: this design beside the Qwen2 decoder of equal size")
     ap.add_argument("--sizes", default="1k,2k,4k", help="with --design: which of the sizes 1k, 2k, 4k (the model's width)")
     ap.add_argument("--gpus", type=int, default=1)

@@ -151,6 +151,66 @@ def oracle_logits(path: str, tokens: list[int]) -> torch.Tensor:
     return _oracle[key]
 
 
+def _bf16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+class Want:
+    """Rows of the oracle's logits with, for each row, the largest change that rounding the activations to
+    bfloat16 causes in the oracle itself (`noise`, absolute).  Small models have rows where a norm divides by a
+    small number or a softmax hangs between two keys: there 8 bits of mantissa move the logits by a tenth of their
+    size, in any implementation; elsewhere by a hundredth.  A bound that scales with the row's own noise stays
+    tight on the ordinary rows."""
+
+    def __init__(self, logits: torch.Tensor, noise: torch.Tensor):
+        self.logits, self.noise = logits, noise
+
+    def __getitem__(self, rows) -> "Want":
+        if isinstance(rows, int):
+            rows = slice(rows, rows + 1)
+        return Want(self.logits[rows], self.noise[rows])
+
+    def __len__(self) -> int:
+        return self.logits.shape[0]
+
+    @staticmethod
+    def cat(parts) -> "Want":
+        return Want(torch.cat([p.logits for p in parts]), torch.cat([p.noise for p in parts]))
+
+
+_wants: dict = {}
+
+
+def oracle(path: str, tokens: list[int]) -> Want:
+    """The oracle's logits at every position and the noise of each row (cached)."""
+    key = (path, tuple(tokens))
+    if key not in _wants:
+        cfg, w = pp.read_folder(path)
+        exact = oracle_logits(path, tokens)
+        rounded = pp.decoder(cfg, w, tokens, torch.float64, rounding=_bf16)
+        _wants[key] = Want(exact, (rounded - exact).abs().amax(dim=1))
+    return _wants[key]
+
+
+def check_rows(got: torch.Tensor, want: Want, dtype: str, what: str, tol: float) -> None:
+    """float32: max |difference| within `tol` of the oracle's largest logit.  bfloat16: row by row within `tol`
+    of the largest logit plus three times the row's own noise."""
+    from helpers import assert_close
+    if dtype != "bfloat16":
+        assert_close(got, want.logits.float(), dtype, what, tol=tol)
+        return
+    got = got.detach().to("cpu", torch.float64)
+    assert got.shape == want.logits.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.logits.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    scale = float(want.logits.abs().max())
+    err = (got - want.logits).abs().amax(dim=1)
+    bound = tol * scale + 3.0 * want.noise
+    over = torch.nonzero(err > bound).flatten().tolist()
+    assert not over, (f"{what}: {len(over)} of {len(err)} rows over their bound, first row {over[0]}: |diff| "
+                      f"{float(err[over[0]]):.3e} > {float(bound[over[0]]):.3e} (largest logit {scale:.3e}, the row's "
+                      f"noise {float(want.noise[over[0]]):.3e}; bfloat16)")
+
+
 def tokens(n: int, vocab: int, seed: int) -> list[int]:
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()

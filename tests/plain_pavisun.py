@@ -89,12 +89,16 @@ def head_slopes(H: int, dtype) -> torch.Tensor:
     return torch.pow(torch.tensor(2.0, dtype=dtype), -8.0 * (torch.arange(H, dtype=dtype) + 1.0) / H)
 
 
+_round = lambda t: t          # set by decoder(rounding=...) for its own run: what a 16-bit engine rounds
+
+
 def softmax_heads(q, k, v, scale, mask, *, cap=None, slopes=None) -> torch.Tensor:
     """q [T, H, d], k [T, G, d], v [T, G, e] -> [T, H * e].  Query head h reads key head h // (H / G).
     score[i, j] = q_i . k_j * scale, then cap * tanh(score / cap) if a cap is given, then minus
     slopes[h] * (i - j) if slopes are given; softmax over the visible j."""
     T, H, _ = q.shape
     G = k.shape[1]
+    q, k, v = _round(q), _round(k), _round(v)
     out = []
     dist = (torch.arange(T).reshape(-1, 1) - torch.arange(T).reshape(1, -1)).to(q.dtype)
     for h in range(H):
@@ -106,7 +110,7 @@ def softmax_heads(q, k, v, scale, mask, *, cap=None, slopes=None) -> torch.Tenso
             s = s - slopes[h] * dist
         s = s.masked_fill(~mask, float("-inf"))
         out.append(torch.softmax(s, dim=-1) @ v[:, g])
-    return torch.cat(out, dim=-1)
+    return _round(torch.cat(out, dim=-1))
 
 
 def rotary_attention(x, w, p, c, positions) -> torch.Tensor:
@@ -138,13 +142,13 @@ def normed_attention(x, w, p, c, eps) -> torch.Tensor:
     m = c.get("mask") or {}
     o = softmax_heads(q, k, v, c["scale"], visible(T, m.get("size"), int(m.get("keep_first", 0))),
                       slopes=head_slopes(H, x.dtype))
-    o = o * torch.sigmoid(x @ w[p + "g"].T)
+    o = _round(o * torch.sigmoid(x @ w[p + "g"].T))
     return o @ w[p + "o"].T
 
 
 def expert(x, w, p):
     """W_down (silu(W_gate x) * (W_up x))."""
-    return (silu(x @ w[p + "gate"].T) * (x @ w[p + "up"].T)) @ w[p + "down"].T
+    return _round(silu(x @ w[p + "gate"].T) * (x @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def table_experts(x, tokens, w, p, c) -> torch.Tensor:
@@ -180,9 +184,21 @@ def schedule(cfg) -> list[int]:
     return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
 
 
-def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, layers_out=None) -> torch.Tensor:
+def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, layers_out=None, rounding=None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence.  `layers_out`: a list that receives the residual stream (the sum of
-    the streams) after every layer run."""
+    the streams) after every layer run.  `rounding`: a function applied to what an engine with 16-bit activations
+    rounds (every sublayer's normed input; q, k and v as the cache holds them; the heads before the output
+    projection; an expert's inner activation; the final norm's result): the difference to the exact logits is
+    the size of error that such rounding alone causes at each position."""
+    global _round
+    _round = rounding or (lambda t: t)
+    try:
+        return _decoder(cfg, weights, tokens, dtype, layers_out)
+    finally:
+        _round = lambda t: t
+
+
+def _decoder(cfg, weights, tokens, dtype, layers_out):
     w = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = cfg["norm"]["eps"]
     T = len(tokens)
@@ -194,10 +210,10 @@ def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, la
     def sublayer(fn, norm_w, hc):
         nonlocal x, xs
         if S:
-            y = fn(rms_norm(stream_read(xs, w, hc), norm_w, eps))
+            y = fn(_round(rms_norm(stream_read(xs, w, hc), norm_w, eps)))
             xs = stream_write(xs, y, w, hc)
         else:
-            x = x + fn(rms_norm(x, norm_w, eps))
+            x = x + fn(_round(rms_norm(x, norm_w, eps)))
 
     for li in schedule(cfg):
         L = cfg["layers"][li]
@@ -215,7 +231,7 @@ def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, la
             layers_out.append((xs.sum(dim=0) if S else x).clone())
     if S:
         x = xs.sum(dim=0)
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = _round(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     cap = cfg.get("logit_softcap")
     return tanh_cap(logits, cap) if cap else logits
 
