@@ -287,11 +287,12 @@ def pavisun_roofline(rec: dict, pk: dict, P: int) -> dict:
     between_q = P * width * (2 * 2 + 2 + 2) * 2 * layers
     roof["pavisun.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(between_p, p["prefill_classes_us"]["norms"])
     roof["qwen2.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(between_q, q["prefill_classes_us"]["norms"])
-    # decoding, 64 sequences that hold P + 16 tokens: a row of keys is read once where the values are the keys
+    # decoding, 64 sequences that hold P + 16 tokens: the window's keys and values (the rotating mixer's values are
+    # its keys before the rotation: rows of their own in the cache), and the kept first tokens
     keys = min(P + 16, Wd)
     row = kv * d * 2
     roof["pavisun.decode_b64.attention.frac_of_hbm"] = frac_hbm(
-        64 * ((keys + K) * 2 * row * n_unit + keys * row * n_rot), p["decode_b64_classes_us"]["attention"])
+        64 * ((keys + K) * 2 * row * n_unit + keys * 2 * row * n_rot), p["decode_b64_classes_us"]["attention"])
     roof["qwen2.decode_b64.attention.frac_of_hbm"] = frac_hbm(
         64 * (P + 16) * 2 * row * layers, q["decode_b64_classes_us"]["attention"])
     roof["pavisun.decode_b64.experts.frac_of_hbm"] = frac_hbm(

@@ -353,6 +353,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
+        // constants of the scores with options, in units of log2 (read once, not per tile)
+        const bool ext_capped = WEIGHTS == FT_SOFTMAX_EXT && opt.softcap > 0.f;
+        const float ext_in = WEIGHTS != FT_SOFTMAX_EXT ? 0.f
+            : (ext_capped ? opt.scale * (2.f * 1.4426950408889634f / opt.softcap) : opt.scale * 1.4426950408889634f);
+        const float ext_cap = ext_capped ? opt.softcap * 1.4426950408889634f : 0.f;
+        const float ext_slope = (WEIGHTS == FT_SOFTMAX_EXT && opt.slopes) ? opt.slopes[h] * 1.4426950408889634f : 0.f;
         for (int it = 0; it < n_tiles && ok; ++it) {
             const int j0 = tile_j0(it);
             if (!ft_wait(ft_smem(&s_full[it & 1]), (it >> 1) & 1, true)) { *failed = 1; ok = false; break; }
@@ -373,22 +379,32 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
             }
             if constexpr (WEIGHTS == FT_SOFTMAX_EXT) {
-                // the scores in units of log2: (cap(score * scale) - slope * distance) * log2 e; masked: -inf
-                const float slope = opt.slopes ? opt.slopes[h] : 0.f;
-                const float tc = opt.softcap > 0.f ? 2.f * 1.4426950408889634f / opt.softcap : 0.f;
-                const bool capped = opt.softcap > 0.f;
-#pragma unroll
-                for (int j = 0; j < FT_BN; ++j) {
-                    const int key = j0 + j;
-                    float x = sv[j] * opt.scale;
-                    if (capped) {
+                // the scores in units of log2: (cap(score * scale) - slope * distance) * log2 e; masked: -inf.
+                // cap(x) = c tanh(x / c) = c (1 - 2 / (e^(2x/c) + 1)); the constants are folded (ext_in, ext_cap),
+                // the distance of key j0 + j is d0 - j with j known at compile time (no conversion per score), and
+                // tiles that every row sees whole skip the comparisons.
+                const float d0 = (float)(p_row - j0);
+                auto weigh = [&](float sc, int j) {
+                    float x;
+                    if (ext_capped) {
                         float r;
-                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(ft_exp2(x * tc) + 1.f));
-                        x = opt.softcap * fmaf(-2.f, r, 1.f);
+                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(ft_exp2(sc * ext_in) + 1.f));
+                        x = fmaf(-2.f * ext_cap, r, ext_cap);
+                    } else {
+                        x = sc * ext_in;
                     }
-                    x = fmaf(-slope, (float)(p_row - key), x) * 1.4426950408889634f;
-                    const bool seen = inside || (key <= j_hi && (key >= j_lo || key < keep));
-                    sv[j] = seen ? x : -INFINITY;
+                    return fmaf(-ext_slope, d0 - (float)j, x);
+                };
+                if (inside) {
+#pragma unroll
+                    for (int j = 0; j < FT_BN; ++j) sv[j] = weigh(sv[j], j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < FT_BN; ++j) {
+                        const int key = j0 + j;
+                        const bool seen = key <= j_hi && (key >= j_lo || key < keep);
+                        sv[j] = seen ? weigh(sv[j], j) : -INFINITY;
+                    }
                 }
             }
             if constexpr (WEIGHTS == FT_SIGMOID) {
