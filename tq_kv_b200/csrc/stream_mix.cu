@@ -22,12 +22,15 @@ struct StreamCoefs {
 
 // grid: one block per row r (token rows[r], or r).  y/mix/write may be null (no write), read may be null
 // (no output).  u is held in shared memory [W] between the sum of squares and the scaling.
-template <typename TO, int VEC>
-__global__ void __launch_bounds__(256)
-streams_step_kernel(float* __restrict__ xs, int S, int T, int W, const float* __restrict__ y,
+// NS: the number of streams where the kernel is built for exactly that many (1 to 4: the streams' values of a
+// thread stay in few registers and three or four blocks share an SM), or SM_MAX_STREAMS for any number up to that.
+template <typename TO, int VEC, int NS>
+__global__ void __launch_bounds__(256, NS <= 3 ? 4 : (NS == 4 ? 3 : 1))
+streams_step_kernel(float* __restrict__ xs, int S_any, int T, int W, const float* __restrict__ y,
                     const float* __restrict__ mix, const float* __restrict__ write, const float* __restrict__ read,
                     const float* __restrict__ norm_w, float eps, TO* __restrict__ out,
                     const int* __restrict__ rows) {
+    const int S = NS < SM_MAX_STREAMS ? NS : S_any;
     extern __shared__ float u_sh[];
     __shared__ float red[32];
     __shared__ StreamCoefs cf;
@@ -46,9 +49,9 @@ streams_step_kernel(float* __restrict__ xs, int S, int T, int W, const float* __
     float* row = xs + (size_t)t * W;
     float ss = 0.f;
     for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
-        float x[SM_MAX_STREAMS][VEC];
+        float x[NS][VEC];
 #pragma unroll
-        for (int s = 0; s < SM_MAX_STREAMS; ++s)
+        for (int s = 0; s < NS; ++s)
             if (s < S) {
                 if constexpr (VEC == 4) {
                     const float4 v = *reinterpret_cast<const float4*>(row + s * stride + i);
@@ -65,21 +68,21 @@ streams_step_kernel(float* __restrict__ xs, int S, int T, int W, const float* __
             } else {
                 yv[0] = y[(size_t)t * W + i];
             }
-            float nx[SM_MAX_STREAMS][VEC];
+            float nx[NS][VEC];
 #pragma unroll
-            for (int to = 0; to < SM_MAX_STREAMS; ++to)
+            for (int to = 0; to < NS; ++to)
                 if (to < S) {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
                         float a = cf.write[to] * yv[e];
 #pragma unroll
-                        for (int s = 0; s < SM_MAX_STREAMS; ++s)
+                        for (int s = 0; s < NS; ++s)
                             if (s < S) a = fmaf(cf.mix[s * S + to], x[s][e], a);
                         nx[to][e] = a;
                     }
                 }
 #pragma unroll
-            for (int s = 0; s < SM_MAX_STREAMS; ++s)
+            for (int s = 0; s < NS; ++s)
                 if (s < S) {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) x[s][e] = nx[s][e];
@@ -96,7 +99,7 @@ streams_step_kernel(float* __restrict__ xs, int S, int T, int W, const float* __
             for (int e = 0; e < VEC; ++e) {
                 float u = 0.f;
 #pragma unroll
-                for (int s = 0; s < SM_MAX_STREAMS; ++s)
+                for (int s = 0; s < NS; ++s)
                     if (s < S) u = fmaf(cf.read[s], x[s][e], u);
                 u_sh[i + e] = u;
                 ss = fmaf(u, u, ss);
@@ -130,18 +133,27 @@ TQ_API int tq_streams_step(float* xs, int S, int T, int W, const float* y, const
     if (!y && !out) return 0;
     const size_t smem = out ? (size_t)W * sizeof(float) : 0;
     const bool vec = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(y)) % 16 == 0);
+#define TQ_LAUNCH_NS(TO, V, NS)                                                                                  \
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, streams_step_kernel<TO, V, NS>, dim3(n_rows), dim3(256), smem,      \
+                         stream, xs, S, T, W, y, mix, write, read, norm_w, eps, (TO*)out, rows)
 #define TQ_LAUNCH(TO, V)                                                                                         \
-    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, streams_step_kernel<TO, V>, dim3(n_rows), dim3(256), smem, stream,  \
-                         xs, S, T, W, y, mix, write, read, norm_w, eps, (TO*)out, rows)
+    switch (S) {                                                                                                 \
+        case 1: TQ_LAUNCH_NS(TO, V, 1);                                                                          \
+        case 2: TQ_LAUNCH_NS(TO, V, 2);                                                                          \
+        case 3: TQ_LAUNCH_NS(TO, V, 3);                                                                          \
+        case 4: TQ_LAUNCH_NS(TO, V, 4);                                                                          \
+        default: TQ_LAUNCH_NS(TO, V, SM_MAX_STREAMS);                                                            \
+    }
     if (out_dtype == TQ_F32 || !out) {
-        if (vec) TQ_LAUNCH(float, 4);
-        TQ_LAUNCH(float, 1);
+        if (vec) TQ_LAUNCH(float, 4)
+        TQ_LAUNCH(float, 1)
     }
     if (out_dtype == TQ_BF16) {
-        if (vec) TQ_LAUNCH(bf16, 4);
-        TQ_LAUNCH(bf16, 1);
+        if (vec) TQ_LAUNCH(bf16, 4)
+        TQ_LAUNCH(bf16, 1)
     }
 #undef TQ_LAUNCH
+#undef TQ_LAUNCH_NS
     return (int)cudaErrorInvalidValue;
 }
 
