@@ -359,6 +359,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             : (ext_capped ? opt.scale * (2.f * 1.4426950408889634f / opt.softcap) : opt.scale * 1.4426950408889634f);
         const float ext_cap = ext_capped ? opt.softcap * 1.4426950408889634f : 0.f;
         const float ext_slope = (WEIGHTS == FT_SOFTMAX_EXT && opt.slopes) ? opt.slopes[h] * 1.4426950408889634f : 0.f;
+        if constexpr (WEIGHTS == FT_SOFTMAX_EXT) {
+            // the row's gate values are wanted when O leaves: ask L2 for them now (lines of 32 floats)
+            if (opt.gate) {
+                const float* gp = opt.gate + (size_t)(tok0 + min(i_row, len - 1)) * opt.ldg + (size_t)h * HD;
+                for (int c = 0; c < HD; c += 32) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(gp + c));
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(gp + HD - 1));
+            }
+        }
         for (int it = 0; it < n_tiles && ok; ++it) {
             const int j0 = tile_j0(it);
             if (!ft_wait(ft_smem(&s_full[it & 1]), (it >> 1) & 1, true)) { *failed = 1; ok = false; break; }
@@ -490,6 +498,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         // The last tile's P·V, then O / l.  (A barrier of its own: the softmax threads no longer follow every
         // phase of p_empty, and a wait by parity cannot tell a phase that is two behind from one that is done.)
+        // The gate's values of the row come in pieces of 32, each loaded while the piece before is applied; the
+        // first is asked for before the wait for the last P·V.
+        const float* grow = (WEIGHTS == FT_SOFTMAX_EXT && opt.gate)
+                                ? opt.gate + (size_t)(tok0 + min(i_row, len - 1)) * opt.ldg + (size_t)h * HD : nullptr;
+        float4 g_next[8];
+        if (WEIGHTS == FT_SOFTMAX_EXT && grow) {
+#pragma unroll
+            for (int d = 0; d < 8; ++d) g_next[d] = *reinterpret_cast<const float4*>(grow + 4 * d);
+        }
         if (ok && !ft_wait(ft_smem(o_done), 0, true)) { *failed = 1; ok = false; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (ok) {
@@ -497,16 +514,21 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if constexpr (WEIGHTS == FT_SIGMOID)
                 inv = gate ? 1.f / (1.f + expf(-gate[(size_t)(tok0 + min(i_row, len - 1)) * ldg + h])) : 1.f;
             bf16* orow = out + ((size_t)(tok0 + min(i_row, len - 1)) * nh + h) * HD;
-            const float* grow = (WEIGHTS == FT_SOFTMAX_EXT && opt.gate)
-                                    ? opt.gate + (size_t)(tok0 + min(i_row, len - 1)) * opt.ldg + (size_t)h * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
                 float v[32];
                 ft_ld32(tmem_o + lane_addr + c, v);           // (all lanes take part in the load)
                 if (WEIGHTS == FT_SOFTMAX_EXT && grow) {
+                    float4 g_now[8];
+#pragma unroll
+                    for (int d = 0; d < 8; ++d) g_now[d] = g_next[d];
+                    if (c + 32 < HD) {
+#pragma unroll
+                        for (int d = 0; d < 8; ++d) g_next[d] = *reinterpret_cast<const float4*>(grow + c + 32 + 4 * d);
+                    }
 #pragma unroll
                     for (int d = 0; d < 32; d += 4) {
-                        const float4 gv = *reinterpret_cast<const float4*>(grow + c + d);
+                        const float4 gv = g_now[d >> 2];
                         v[d] = __fdividef(v[d], 1.f + __expf(-gv.x));
                         v[d + 1] = __fdividef(v[d + 1], 1.f + __expf(-gv.y));
                         v[d + 2] = __fdividef(v[d + 2], 1.f + __expf(-gv.z));
