@@ -26,7 +26,7 @@ from ..cache import PAGE_TOKENS
 from .batch import StepRow
 from .engine import Engine
 
-SLACK_PAGES = 32
+SLACK_PAGES = 64
 
 
 class TraceError(ValueError):
