@@ -288,6 +288,36 @@ def test_rows_that_hang_on_planted_keys_in_prompts_portions_and_decoding(tmp_roo
     assert eng.cache.free_slots == eng.cache.max_slots
 
 
+# Heads whose widths are no multiples of 8 (the kernels' rows are then padded inside): keys of 20 with 10 rotated
+# entries, unit-size keys of 12 beside values of 20 and of 4, one layer run twice.
+P_ODD = _model(200, 72, 1e-5, [
+    {**_rot(3, 1, 20, 50, 0.3, cap=10.0, dims=10, scaling=(4.0, 32, 8.0, 1.0)), "mlp": None},
+    {**_unit(2, 2, 12, 20, 40, 3, 1.2), "mlp": None},
+    {**_unit(4, 2, 36, 4, None, 0, 0.9), "mlp": None},
+], streams=2, loop=(1, 2, 2), cap=15.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_widths_that_are_no_multiple_of_8(tmp_root, dtype):
+    from tq_kv_b200.engine import StepRow
+    path = pp.write_folder(os.path.join(str(tmp_root), "odd_heads"), P_ODD, make_weights(P_ODD, 21))
+    eng = _engine(path, dtype)
+    a, b = tokens(150, 200, 31), tokens(70, 200, 32)
+    wa, wb = oracle(path, a), oracle(path, b)
+    s = eng.new_sequence()
+    _check(eng.step([StepRow(s, a, list(range(150)))]), wa, dtype, "odd heads whole")
+    eng.release(s)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([StepRow(sa, a[:100], [99]), StepRow(sb, b[:20], [19])])
+    got_a, got_b = [out[:1]], [out[1:]]
+    for t in range(50):
+        out = eng.step([StepRow(sa, [a[100 + t]], [0]), StepRow(sb, [b[20 + t]], [0])])
+        got_a.append(out[:1])
+        got_b.append(out[1:])
+    _check(torch.cat(got_a), wa[99:], dtype, "odd heads batch row 0")
+    _check(torch.cat(got_b), wb[19:], dtype, "odd heads batch row 1")
+
+
 # ---- the entry points -------------------------------------------------------------------------------------------
 def test_greedy_generation_through_the_entry_point_and_the_command_line(tmp_root):
     import tq_kv_b200 as tq

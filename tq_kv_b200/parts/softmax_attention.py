@@ -16,7 +16,8 @@
   output_gate       the heads side by side are multiplied entry by entry with
                     sigmoid(W_g x) before the output projection
 Query head h reads key/value head h // (heads / kv_heads).  Key rows and value rows
-may differ in width.  No biases.
+may differ in width; widths that are no multiple of 8 are padded with zeros inside.
+No biases.
 
 All projections are one product with the concatenated weight (float32 result); one
 kernel encodes q and k, splits the heads and appends k and v to the cache
@@ -50,18 +51,31 @@ class SoftmaxAttention(Mixer):
         self.hidden = int(p["hidden_size"])
         self.n_heads = int(p["num_heads"])
         self.n_kv_heads = int(p["num_kv_heads"])
-        self.key_dim = int(p["key_dim"])
+        # The kernels take rows of whole 16-byte pieces: heads of other widths (`key_dim_given`, `value_dim_given`)
+        # are padded to the next multiple of 8 with zero rows of W_q, W_k, W_v, W_g and zero columns of W_o, which
+        # changes no score and no result (a mean over a head's entries is corrected below).
+        self.key_dim_given = int(p["key_dim"])
         self.values = p.get("values", "projected")
         if self.values not in ("projected", "keys"):
             raise ConfigError(f"softmax attention: values '{self.values}' (projected or keys)")
-        self.value_dim = int(p.get("value_dim") or self.key_dim)
-        if self.values == "keys" and self.value_dim != self.key_dim:
-            raise ConfigError(f"softmax attention: values that are the keys have the keys' width {self.key_dim}, "
-                              f"not {self.value_dim}")
+        self.value_dim_given = int(p.get("value_dim") or self.key_dim_given)
+        if self.values == "keys" and self.value_dim_given != self.key_dim_given:
+            raise ConfigError(f"softmax attention: values that are the keys have the keys' width "
+                              f"{self.key_dim_given}, not {self.value_dim_given}")
+        if self.key_dim_given < 1 or self.value_dim_given < 1:
+            raise ConfigError("softmax attention: heads need at least one entry")
+        self.key_dim = -(-self.key_dim_given // 8) * 8
+        self.value_dim = -(-self.value_dim_given // 8) * 8
         self.scale = float(p["scale"])
         self.softcap = float(p["softcap"]) if p.get("softcap") else None
         self.slope_exponent = float(p["slope_exponent"]) if p.get("slope_exponent") else None
         self.qk_norm_eps = float(p["qk_norm_eps"]) if p.get("qk_norm_eps") else 0.0
+        if self.qk_norm_eps and self.key_dim != self.key_dim_given:
+            # the kernel's mean runs over d' = key_dim entries of which d = key_dim_given are not zero:
+            # x / sqrt(sum / d + eps) = sqrt(d / d') * x / sqrt(sum / d' + eps * d / d'), for q and for k
+            ratio = self.key_dim_given / self.key_dim
+            self.qk_norm_eps *= ratio
+            self.scale *= ratio
         self.window: Optional[int] = int(p["window"]) if p.get("window") else None
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
         self.output_gate = bool(p.get("output_gate", False))
@@ -71,8 +85,9 @@ class SoftmaxAttention(Mixer):
         if self.position is not None:
             if getattr(self.position, "layout", None) != "halves":
                 raise ConfigError("softmax attention rotates in the 'halves' layout (a rotary_tables part)")
-            if self.position.rotary_dim > self.key_dim:
-                raise ConfigError(f"softmax attention: {self.position.rotary_dim} rotated entries in heads of {self.key_dim}")
+            if self.position.rotary_dim > self.key_dim_given:
+                raise ConfigError(f"softmax attention: {self.position.rotary_dim} rotated entries in heads of "
+                                  f"{self.key_dim_given}")
             if self.qk_norm_eps:
                 raise ConfigError("softmax attention: either a rotation or unit-size q and k, not both")
         self.q_width = self.n_heads * self.key_dim
@@ -87,22 +102,39 @@ class SoftmaxAttention(Mixer):
         return f"{self.prefix}{self.names[which]}"
 
     def weight_specs(self):
-        specs = [WeightSpec(self._n("q"), (self.q_width, self.hidden), "matrix"),
-                 WeightSpec(self._n("k"), (self.k_width, self.hidden), "matrix")]
+        d, e, H, G = self.key_dim_given, self.value_dim_given, self.n_heads, self.n_kv_heads
+        specs = [WeightSpec(self._n("q"), (H * d, self.hidden), "matrix"),
+                 WeightSpec(self._n("k"), (G * d, self.hidden), "matrix")]
         if self.values == "projected":
-            specs.append(WeightSpec(self._n("v"), (self.v_width, self.hidden), "matrix"))
+            specs.append(WeightSpec(self._n("v"), (G * e, self.hidden), "matrix"))
         if self.output_gate:
-            specs.append(WeightSpec(self._n("gate"), (self.o_width, self.hidden), "matrix"))
-        specs.append(WeightSpec(self._n("out"), (self.hidden, self.o_width), "matrix"))
+            specs.append(WeightSpec(self._n("gate"), (H * e, self.hidden), "matrix"))
+        specs.append(WeightSpec(self._n("out"), (self.hidden, H * e), "matrix"))
         return specs
+
+    @staticmethod
+    def _pad_heads(w: torch.Tensor, heads: int, given: int, padded: int) -> torch.Tensor:
+        """[heads * given, W] -> [heads * padded, W] with zero rows behind every head's own."""
+        if given == padded:
+            return w
+        out = w.new_zeros((heads, padded, w.shape[1]))
+        out[:, :given] = w.reshape(heads, given, w.shape[1])
+        return out.reshape(heads * padded, w.shape[1])
 
     def bind(self, tensors, runtime: Runtime, shared: Optional[dict] = None):
         which = ["q", "k"] + (["v"] if self.values == "projected" else []) + (["gate"] if self.output_gate else [])
-        ws = [tensors[self._n(x)] for x in which]
+        heads = {"q": (self.n_heads, self.key_dim_given, self.key_dim),
+                 "k": (self.n_kv_heads, self.key_dim_given, self.key_dim),
+                 "v": (self.n_kv_heads, self.value_dim_given, self.value_dim),
+                 "gate": (self.n_heads, self.value_dim_given, self.value_dim)}
+        ws = [self._pad_heads(tensors[self._n(x)], *heads[x]) for x in which]
         if len({w.dtype for w in ws}) != 1:
             ws = [w.to(torch.float32) for w in ws]
         self.w_in = torch.cat(ws, dim=0).contiguous()        # one product: [q | k | (v) | (gate)]
-        self.w_o = tensors[self._n("out")].contiguous()
+        w_o = tensors[self._n("out")]
+        if self.value_dim != self.value_dim_given:           # zero columns where the heads were padded
+            w_o = self._pad_heads(w_o.t(), self.n_heads, self.value_dim_given, self.value_dim).t()
+        self.w_o = w_o.contiguous()
         self.k_col = self.q_width
         self.v_col = self.k_col + self.k_width if self.values == "projected" else -1
         self.g_col = self.q_width + self.k_width + self.v_width
