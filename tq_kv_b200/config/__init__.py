@@ -1,4 +1,7 @@
 """Typed configuration, the architecture registry and the named shapes."""
+from .furesun import ARCHITECTURE as FURESUN_ARCHITECTURE
+from .furesun import MODEL_TYPE as FURESUN_MODEL_TYPE
+from .furesun import FuresunConfig, build_furesun_spec
 from .model_spec import ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .pavisun import ARCHITECTURE as PAVISUN_ARCHITECTURE
 from .pavisun import MODEL_TYPE as PAVISUN_MODEL_TYPE
@@ -28,7 +31,11 @@ register_architecture(
 register_architecture(
     Architecture(PAVISUN_ARCHITECTURE, PAVISUN_MODEL_TYPE, PavisunConfig, build_pavisun_spec), replace=True)
 
+register_architecture(
+    Architecture(FURESUN_ARCHITECTURE, FURESUN_MODEL_TYPE, FuresunConfig, build_furesun_spec), replace=True)
+
 __all__ = [
+    "FuresunConfig", "build_furesun_spec",
     "PavisunConfig", "build_pavisun_spec",
     "RirudraConfig", "build_rirudra_spec",
     "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "ScheduleEntry",

@@ -12,7 +12,9 @@
 // Options beyond the reference (AttnOptions; all off by default): value rows
 // of another width than the keys; a cap on the scores, s <- cap * tanh(s / cap);
 // a bias that grows with the distance, s <- s - slope[h] * (p - j); and first
-// tokens that stay visible behind the window (keys j < keep_first).
+// tokens that stay visible behind the window (keys j < keep_first); a sink in
+// the softmax: one more key of score 0 that has no value, i.e. one added to the
+// softmax's denominator (in the merge step where the keys are split).
 #include "common.cuh"
 
 #define ATT_MAX_PAIRS 8   // head_dim <= 512: each lane owns up to 8 pairs of dims
@@ -35,6 +37,7 @@ struct AttnOptions {
     float softcap;          // > 0: scores become softcap * tanh(score / softcap)
     const float* slopes;    // [nh] or null: score -= slopes[h] * (query position - key position)
     int keep_first;         // with a window: keys below this position stay visible
+    int sink;               // != 0: the softmax's denominator counts one more key of score 0 (it has no value)
 };
 
 template <typename TC>
@@ -140,6 +143,13 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
         }
 
         if (n_splits == 1) {
+            if (opt.sink) {                                  // the sink's exp(0 - m), with the maximum moved up to 0
+                const float m_new = fmaxf(m, 0.f);
+                const float corr = expf(m - m_new);
+                l = l * corr + expf(-m_new);
+#pragma unroll
+                for (int i = 0; i < 2 * ATT_MAX_PAIRS; ++i) acc[i] *= corr;
+            }
             const float inv = 1.f / l;
             TC* o = out + ((size_t)t * nh + h) * vd;
 #pragma unroll
@@ -165,7 +175,7 @@ __global__ void attention_kernel(const TC* __restrict__ q, KVSource src, const i
 // scheduling.  An empty split has m = -inf and l = 0 and contributes nothing.
 template <typename TC>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                       TC* __restrict__ out, int nh, int hd, int n_splits) {
+                                       TC* __restrict__ out, int nh, int hd, int n_splits, int sink) {
     const size_t r0 = ((size_t)blockIdx.x * nh + blockIdx.y) * n_splits;
     const int lane = threadIdx.x & 31;
     pdl_wait();
@@ -174,12 +184,14 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     float m = -INFINITY;
     for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, part_ml[2 * (r0 + s)]);
     m = warp_max(m);
+    if (sink) m = fmaxf(m, 0.f);                    // the sink is one more split: maximum 0, sum 1, no values
     float l = 0.f;
     for (int s = lane; s < n_splits; s += 32) {
         const float ms = part_ml[2 * (r0 + s)];
         if (ms > -INFINITY) l += part_ml[2 * (r0 + s) + 1] * expf(ms - m);
     }
     l = warp_sum(l);
+    if (sink) l += expf(-m);
     TC* o = out + ((size_t)blockIdx.x * nh + blockIdx.y) * hd;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.f;
@@ -201,7 +213,7 @@ TQ_API int tq_attention_ext(const void* q, int dtype, const void* k_packed, cons
                             int page_tokens, const int* tok_pos, const int* tok_seq, const int* cu_seqlens,
                             const int* start_pos, int window, float scale, void* out, float* part_acc, float* part_ml,
                             int n_tokens, int nh, int nkv, int hd, int vd, float softcap, const float* slopes,
-                            int keep_first, int n_splits, cudaStream_t stream) {
+                            int keep_first, int sink, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > 64 * ATT_MAX_PAIRS || hd % 8 || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (vd <= 0 || vd > 64 * ATT_MAX_PAIRS || vd % 8 || keep_first < 0) return (int)cudaErrorInvalidValue;
@@ -210,7 +222,7 @@ TQ_API int tq_attention_ext(const void* q, int dtype, const void* k_packed, cons
     if (!k_packed && (!k_pages || !block_table || page_tokens <= 0)) return (int)cudaErrorInvalidValue;
     if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorInvalidValue;
     KVSource src{k_packed, v_packed, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens};
-    AttnOptions opt{vd, softcap, slopes, window > 0 ? keep_first : 0};
+    AttnOptions opt{vd, softcap, slopes, window > 0 ? keep_first : 0, sink};
     const int n_rep = nh / nkv;
     const int n_warps = n_rep < 8 ? n_rep : 8;
     const dim3 grid(n_tokens, nkv, n_splits);
@@ -229,9 +241,9 @@ TQ_API int tq_attention_ext(const void* q, int dtype, const void* k_packed, cons
     if (st || n_splits == 1) return st;
     const dim3 mgrid(n_tokens, nh);
     if (dtype == TQ_F32)
-        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, vd, n_splits);
+        attention_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (float*)out, nh, vd, n_splits, sink);
     else
-        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, vd, n_splits);
+        attention_merge_kernel<bf16><<<mgrid, 128, 0, stream>>>(part_acc, part_ml, (bf16*)out, nh, vd, n_splits, sink);
     return tq_launch_status();
 }
 
@@ -243,20 +255,20 @@ TQ_API int tq_attention(const void* q, int dtype, const void* k_packed, const vo
     if (hd % 16) return (int)cudaErrorInvalidValue;
     return tq_attention_ext(q, dtype, k_packed, v_packed, k_pages, v_pages, block_table, table_width, ring_pages,
                             page_tokens, tok_pos, tok_seq, cu_seqlens, start_pos, window, scale, out, part_acc,
-                            part_ml, n_tokens, nh, nkv, hd, hd, 0.f, nullptr, 0, n_splits, stream);
+                            part_ml, n_tokens, nh, nkv, hd, hd, 0.f, nullptr, 0, 0, n_splits, stream);
 }
 
 // The merge step alone, for kernels that write (unnormalised output, max, sum) per split themselves.
 TQ_API int tq_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_tokens, int nh,
-                              int hd, int n_splits, cudaStream_t stream) {
+                              int hd, int n_splits, int sink, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_splits < 1 || !part_acc || !part_ml) return (int)cudaErrorInvalidValue;
     const dim3 mgrid(n_tokens, nh);
     if (dtype == TQ_F32)
         return tq_launch_pdl(TQ_PDL_MERGE, attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
-                             (float*)out, nh, hd, n_splits);
+                             (float*)out, nh, hd, n_splits, sink);
     if (dtype == TQ_BF16)
         return tq_launch_pdl(TQ_PDL_MERGE, attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, part_acc, part_ml,
-                             (bf16*)out, nh, hd, n_splits);
+                             (bf16*)out, nh, hd, n_splits, sink);
     return (int)cudaErrorInvalidValue;
 }

@@ -28,7 +28,7 @@ GROUPS: dict[str, list[str]] = {
     # everything a model needs in either precision
     "core": ["elementwise.cu", "attention.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "gemm.cu", "skinny_gemm.cu",
              "gemm_tc.cu", "decode_gemm_tc.cu", "sampling.cu", "random_fill.cu", "linear_scan.cu", "sigmoid_attention.cu",
-             "short_conv.cu", "latent_attention.cu", "head_encode.cu", "stream_mix.cu", "routed_experts.cu"],
+             "short_conv.cu", "latent_attention.cu", "head_encode.cu", "stream_mix.cu", "routed_experts.cu", "mlstm.cu"],
     # decode attention for callers that cannot allocate: a library of its own (flash_decode_static.h)
     "noalloc": ["flash_decode_static.cu"],
     # the host side of a step: cache bookkeeping, checks and packing (C++, no CUDA: builds and runs without a GPU)

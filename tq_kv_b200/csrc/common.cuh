@@ -106,6 +106,24 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// The activation of a gated feed-forward, act(gate) * up.  TQ_ACT_SILU: z * sigmoid(z); TQ_ACT_GELU_TANH:
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).  The `_fast` forms use the special-function unit's exponential
+// and division (a couple of float32 ulp: for results that are rounded to bfloat16).
+#define TQ_ACT_SILU 1
+#define TQ_ACT_GELU_TANH 2
+__device__ __forceinline__ float gated_act(float z, int act) {
+    if (act == TQ_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+__device__ __forceinline__ float gated_act_fast(float z, int act) {
+    if (act == TQ_ACT_GELU_TANH) {
+        // 0.5 z (1 + tanh(u)) = z / (1 + exp(-2u))
+        const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+        return __fdividef(z, 1.f + __expf(-2.f * u));
+    }
+    return __fdividef(z, 1.f + __expf(-z));
+}
+
 static inline int tq_launch_status() { return (int)cudaGetLastError(); }
 
 // Streaming multiprocessors of the current device (asked once per device): grids and splits are sized by it.

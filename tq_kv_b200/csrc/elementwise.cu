@@ -383,26 +383,26 @@ TQ_API int tq_qkv_rope_cache(const void* qkv, int in_dtype, const float* bias, c
 // first, then the up columns.
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
-__global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, size_t total, int act) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int i = (int)(idx - t * I);
         const float g = to_f32<TI>(gu[t * 2 * I + i]);
         const float u = to_f32<TI>(gu[t * 2 * I + I + i]);
-        const float s = g / (1.f + expf(-g));
-        out[idx] = from_f32<TO>(s * u);
+        out[idx] = from_f32<TO>(gated_act(g, act) * u);
     }
 }
 
-TQ_API int tq_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int I, cudaStream_t stream) {
+TQ_API int tq_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int I, int act,
+                     cudaStream_t stream) {
     const size_t total = (size_t)n_rows * I;
     if (total == 0) return 0;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > (size_t)tq_sm_count() * 32) blocks = (size_t)tq_sm_count() * 32;
 #define TQ_LAUNCH(TI, TO) \
-    swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, I, total)
+    swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, I, total, act)
     if (in_dtype == TQ_F32 && out_dtype == TQ_F32) TQ_LAUNCH(float, float);
     else if (in_dtype == TQ_F32 && out_dtype == TQ_BF16) TQ_LAUNCH(float, bf16);
     else if (in_dtype == TQ_BF16 && out_dtype == TQ_BF16) TQ_LAUNCH(bf16, bf16);
@@ -601,6 +601,60 @@ TQ_API int tq_add_normed(float* acc, const float* x0, const float* w0, const flo
     const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, add_normed_kernel, dim3(n_rows), dim3(threads), 0, stream, acc, s, W, eps,
                          scale);
+}
+
+// ---------------------------------------------------------------------------
+// The residual sum of a layer that norms what its sublayers give:  acc[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w,
+// and, if asked, the sum rounded to the activations' type for the next sublayer, which reads the stream itself.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void add_normed_copy_kernel(float* __restrict__ acc, const float* __restrict__ y, const float* __restrict__ w,
+                                       int W, float eps, TO* __restrict__ copy) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
+    const float* yr = y + (size_t)t * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)W + eps);
+    float* a = acc + (size_t)t * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = a[i] + (yr[i] * inv) * w[i];
+        a[i] = v;
+        if (copy) copy[(size_t)t * W + i] = from_f32<TO>(v);
+    }
+}
+
+TQ_API int tq_add_normed_copy(float* acc, const float* y, const float* w, int n_rows, int W, float eps, void* copy,
+                              int copy_dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!acc || !y || !w || W <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+    if (copy && copy_dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, add_normed_copy_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, acc,
+                             y, w, W, eps, (bf16*)copy);
+    if (copy && copy_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, add_normed_copy_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, acc, y,
+                         w, W, eps, (float*)copy);
+}
+
+// out[i] = bfloat16(x[i]): float32 rows rounded for a reader that takes the activations' type.
+__global__ void round_rows_kernel(const float* __restrict__ x, bf16* __restrict__ out, size_t total) {
+    pdl_wait();
+    pdl_launch();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = __float2bfloat16_rn(x[idx]);
+}
+
+TQ_API int tq_round_rows(const float* x, void* out, size_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > (size_t)tq_sm_count() * 16) blocks = (size_t)tq_sm_count() * 16;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, round_rows_kernel, dim3((int)blocks), dim3(256), 0, stream, x, (bf16*)out,
+                         total);
 }
 
 // ---------------------------------------------------------------------------

@@ -60,6 +60,7 @@ struct FdOptions {
     float softcap;          // > 0: scores become softcap * tanh(score / softcap)
     const float* slopes;    // [nh] or null
     int keep_first;         // with a window: keys below this position stay visible
+    int sink;               // != 0: one added to the softmax's denominator (a key of score 0 without a value)
 };
 
 // cap * tanh(x / cap) with 2^x and the reciprocal of the special-function unit (a few ulp; tanh.approx is not enough)
@@ -351,6 +352,11 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
         const int h = g * n_rep + r;
         if (n_splits == 1) {
+            if (WEIGHTS == FD_SOFTMAX_EXT && opt.sink) {      // (with splits the merge step adds the sink)
+                const float m2 = fmaxf(m, 0.f), f = exp2f(m - m2);
+                l = l * f + exp2f(-m2);
+                a *= f;
+            }
             out[((size_t)t * nh + h) * HD + d] = __float2bfloat16_rn(a / l);
         } else {
             const size_t pr = ((size_t)t * nh + h) * n_splits + split;
@@ -473,9 +479,9 @@ TQ_API int tq_sigmoid_flash_decode(const void* q, const void* k_pages, const voi
 // cache that keeps all keys (no ring).  Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach.
 TQ_API int tq_flash_decode_ext(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                int table_width, int ring_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
-                               int window, float scale, float softcap, const float* slopes, int keep_first, void* out,
-                               float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int hd, int n_splits,
-                               cudaStream_t stream) {
+                               int window, float scale, float softcap, const float* slopes, int keep_first, int sink,
+                               void* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int hd,
+                               int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv || page_tokens != FD_PAGE) return (int)cudaErrorNotSupported;
     if (keep_first < 0 || (keep_first > 0 && ring_pages > 0)) return (int)cudaErrorInvalidValue;
@@ -485,7 +491,7 @@ TQ_API int tq_flash_decode_ext(const void* q, const void* k_pages, const void* v
     nkv *= kv_div;
     if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorNotSupported;
     if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
-    const FdOptions opt{scale, softcap, slopes, window > 0 ? keep_first : 0};
+    const FdOptions opt{scale, softcap, slopes, window > 0 ? keep_first : 0, sink};
 #define TQ_FD(H)                                                                                                        \
     case H:                                                                                                             \
         return launch_flash_decode<H, FD_SOFTMAX_EXT>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages,      \

@@ -86,5 +86,5 @@ int tq_flash_decode_static(const void* q, const void* k_pages, const void* v_pag
         return TQ_STATIC_UNSUPPORTED;
     }
     if (st || n_splits == 1) return st;
-    return tq_attention_merge(part_acc, part_ml, out, TQ_BF16, n_tokens, n_heads, head_dim, n_splits, stream);
+    return tq_attention_merge(part_acc, part_ml, out, TQ_BF16, n_tokens, n_heads, head_dim, n_splits, 0, stream);
 }

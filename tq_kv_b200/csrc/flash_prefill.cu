@@ -64,6 +64,7 @@ struct FpOptions {
     int keep_first;
     const float* gate;      // float32 logits [T, ldg] (column h * HD + d) or null
     int ldg;
+    int sink;               // != 0: one added to the softmax's denominator (a key of score 0 without a value)
 };
 
 // cap * tanh(x / cap) with 2^x and a fast division (a few ulp; tanh.approx is not enough)
@@ -280,7 +281,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, FpSource src, const int* __rest
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (ri[r] >= len) continue;
-        const float inv = 1.f / l_run[r];
+        // (the sink's share of the denominator is 2^(0 - m) in the units the sums are kept in)
+        const float inv = 1.f / ((EXT && opt.sink) ? l_run[r] + exp2f(-m_run[r]) : l_run[r]);
         bf16* orow = out + ((size_t)(tok0 + ri[r]) * nh + h) * HD;
         const float* grow = (EXT && opt.gate) ? opt.gate + (size_t)(tok0 + ri[r]) * opt.ldg + (size_t)h * HD : nullptr;
 #pragma unroll
@@ -347,14 +349,15 @@ TQ_API int tq_flash_prefill_ext(const void* q, const void* k_packed, const void*
                                 const void* v_pages, const int* block_table, int table_width, int ring_pages,
                                 int page_tokens, const int* cu_seqlens, const int* start_pos, int n_seqs, int n_tokens,
                                 int window, float scale, float softcap, const float* slopes, int keep_first,
-                                const float* gate, int ldg, void* out, int nh, int nkv, int hd, cudaStream_t stream) {
+                                int sink, const float* gate, int ldg, void* out, int nh, int nkv, int hd,
+                                cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh > 65535) return (int)cudaErrorNotSupported;
     if (!k_packed && (!k_pages || !block_table || page_tokens <= 0)) return (int)cudaErrorInvalidValue;
     if (keep_first < 0 || (keep_first > 0 && !k_packed && ring_pages > 0)) return (int)cudaErrorInvalidValue;
     FpSource src{(const bf16*)k_packed, (const bf16*)v_packed, (const bf16*)k_pages, (const bf16*)v_pages,
                  block_table, table_width, ring_pages, page_tokens};
-    const FpOptions opt{scale, softcap, slopes, keep_first, gate, ldg};
+    const FpOptions opt{scale, softcap, slopes, keep_first, gate, ldg, sink};
 #define TQ_FP(H)                                                                                                    \
     case H:                                                                                                         \
         return launch_flash_prefill<H, true>((const bf16*)q, src, cu_seqlens, start_pos, n_seqs, n_tokens, window, \

@@ -173,6 +173,7 @@ struct FtOptions {
     int keep_first;
     const float* gate;      // float32 logits [T, ldg] (column h * HD + d) or null
     int ldg;
+    int sink;               // != 0: one added to the softmax's denominator (a key of score 0 without a value)
 };
 
 template <int HD, bool PAGED, int WEIGHTS>
@@ -511,6 +512,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (ok) {
             float inv = 1.f / l_run;
+            if constexpr (WEIGHTS == FT_SOFTMAX_EXT) {         // the sink's share: 2^(0 - m_ref), the sums' unit
+                if (opt.sink) inv = 1.f / (l_run + exp2f(-m_ref));
+            }
             if constexpr (WEIGHTS == FT_SIGMOID)
                 inv = gate ? 1.f / (1.f + expf(-gate[(size_t)(tok0 + min(i_row, len - 1)) * ldg + h])) : 1.f;
             bf16* orow = out + ((size_t)(tok0 + min(i_row, len - 1)) * nh + h) * HD;
@@ -667,7 +671,7 @@ TQ_API int tq_flash_prefill_tc_ext(const void* q, const void* k_packed, const vo
                                    const void* v_pages, long long n_pages, const int* block_table, int table_width,
                                    int ring_pages, int page_tokens, const int* cu_seqlens, const int* start_pos,
                                    int n_seqs, int n_tokens, int window, float scale, float softcap,
-                                   const float* slopes, int keep_first, const float* gate, int ldg, void* out, int nh,
+                                   const float* slopes, int keep_first, int sink, const float* gate, int ldg, void* out, int nh,
                                    int nkv, int hd, int* status, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (nkv <= 0 || nh % nkv || (hd != 64 && hd != 128)) return (int)cudaErrorNotSupported;
@@ -687,7 +691,7 @@ TQ_API int tq_flash_prefill_tc_ext(const void* q, const void* k_packed, const vo
         if (!st) st = ft_map(&mv, v_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
     }
     if (st) return st;
-    const FtOptions opt{scale, softcap, slopes, keep_first, gate, ldg};
+    const FtOptions opt{scale, softcap, slopes, keep_first, gate, ldg, sink};
 #define TQ_FT(H, P) return ft_launch<H, P, FT_SOFTMAX_EXT>(mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, \
                                                            start_pos, n_seqs, n_tokens, window, scale, (bf16*)out, nh,    \
                                                            nkv, status, stream, nullptr, 0, nullptr, 0, opt)

@@ -113,7 +113,7 @@ TQ_API int tq_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dtype,
 template <typename TA, typename TW, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
-                 TO* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, int accumulate) {
+                 TO* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, int accumulate, int act) {
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * GV_WARPS + (threadIdx.x >> 5);
     if (n >= N) return;
@@ -174,7 +174,7 @@ gemv_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
             if (lane == 0) {
                 if (bias) { v0 += bias[n]; if (SWIGLU) v1 += bias[n + N]; }
                 float v = v0;
-                if (SWIGLU) v = (v0 / (1.f + expf(-v0))) * v1;
+                if (SWIGLU) v = gated_act(v0, act) * v1;
                 TO* c = C + (size_t)(m0 + r) * ldc + n;
                 if (accumulate) v += to_f32<TO>(*c);
                 *c = from_f32<TO>(v);
@@ -183,7 +183,8 @@ gemv_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
     }
 }
 
-// N is the number of output columns; with swiglu != 0, W has 2*N rows.
+// N is the number of output columns; with swiglu != 0, W has 2*N rows and swiglu names the gate's activation
+// (TQ_ACT_SILU = 1, TQ_ACT_GELU_TANH = 2).
 TQ_API int tq_gemv_rows(const void* A, int a_dtype, const void* W, int w_dtype, const float* bias, void* C,
                         int c_dtype, int M, int N, int K, int lda, int ldw, int ldc, int accumulate, int swiglu,
                         cudaStream_t stream) {
@@ -195,10 +196,10 @@ TQ_API int tq_gemv_rows(const void* A, int a_dtype, const void* W, int w_dtype, 
     do {                                                                                                       \
         if (swiglu)                                                                                            \
             gemv_rows_kernel<TA, TW, TO, true><<<grid, GV_WARPS * 32, 0, stream>>>(                           \
-                (const TA*)A, (const TW*)W, bias, (TO*)C, M, N, K, lda, ldw, ldc, accumulate);                 \
+                (const TA*)A, (const TW*)W, bias, (TO*)C, M, N, K, lda, ldw, ldc, accumulate, swiglu);         \
         else                                                                                                   \
             gemv_rows_kernel<TA, TW, TO, false><<<grid, GV_WARPS * 32, 0, stream>>>(                          \
-                (const TA*)A, (const TW*)W, bias, (TO*)C, M, N, K, lda, ldw, ldc, accumulate);                 \
+                (const TA*)A, (const TW*)W, bias, (TO*)C, M, N, K, lda, ldw, ldc, accumulate, 0);              \
     } while (0)
     const int code = a_dtype * 4 + w_dtype * 2 + c_dtype;
     switch (code) {

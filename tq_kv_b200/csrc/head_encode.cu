@@ -6,8 +6,13 @@
 //   q and k heads (hd entries each) are either rotated by position (rotate-half
 //   layout: entry i < rot/2 is paired with entry i + rot/2; cosine and sine
 //   come from tables [positions, rot/2], which may carry a common factor;
-//   entries from `rot` on pass) or, with norm_eps > 0, divided by their root
-//   mean square, x / sqrt(mean(x^2) + norm_eps), or left as they are;
+//   entries from `rot` on pass; with `paired` the neighbours 2i and 2i + 1 are
+//   a pair instead) or, with norm_eps > 0, divided by their root
+//   mean square, x / sqrt(mean(x^2) + norm_eps), or left as they are; with
+//   `row_inv` (float32 [T, 2]: one factor per token for its whole q row and
+//   one for its whole k row, made by row_inv_rms below) and weights over those
+//   whole rows, q and k are first multiplied by factor * weight: an RMS norm
+//   over the whole projection, before the heads are split and turned;
 //   v heads (vd entries each) are copied: from their own columns, or — v_col < 0
 //   — from the k columns as projected, before the rotation (vd == hd then).
 //
@@ -31,7 +36,8 @@ head_encode_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col,
                    const int* __restrict__ new_lens, const int* __restrict__ block_table, int table_width,
                    int ring_pages, int page_tokens, TC* __restrict__ q_out, TC* __restrict__ k_out,
                    TC* __restrict__ v_out, TC* __restrict__ k_pages, TC* __restrict__ v_pages, int nh, int nkv,
-                   int hd, int vd) {
+                   int hd, int vd, const float* __restrict__ row_inv, const float* __restrict__ q_w,
+                   const float* __restrict__ k_w, int paired) {
     // grid (token, groups of four heads), a warp per head: heads 0..nh-1 are q, then nkv k heads, then nkv v heads
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
@@ -78,21 +84,28 @@ head_encode_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col,
         ss = warp_sum(ss);
         inv = 1.f / sqrtf(ss / (float)width + norm_eps);
     }
+    const float* w = nullptr;                                // the whole-row norm's weights of this head
+    if (row_inv) {
+        inv = row_inv[2 * t + (is_q ? 0 : 1)];
+        w = (is_q ? q_w : k_w) + (size_t)g * hd;
+    }
     const int half = rot >> 1;
     if (half > 0) {
         const float* cs = cos_tab + (size_t)pos * half;
         const float* sn = sin_tab + (size_t)pos * half;
         for (int j = lane; j < half; j += 32) {
-            const float x0 = x[j] * inv, x1 = x[j + half] * inv;
+            const int i0 = paired ? 2 * j : j, i1 = paired ? 2 * j + 1 : j + half;
+            float x0 = x[i0] * inv, x1 = x[i1] * inv;
+            if (w) { x0 *= w[i0]; x1 *= w[i1]; }
             const float c = cs[j], s = sn[j];
             const TC r0 = from_f32<TC>(x0 * c - x1 * s);
             const TC r1 = from_f32<TC>(x1 * c + x0 * s);
-            if (dst) { dst[j] = r0; dst[j + half] = r1; }
-            if (cache) { cache[j] = r0; cache[j + half] = r1; }
+            if (dst) { dst[i0] = r0; dst[i1] = r1; }
+            if (cache) { cache[i0] = r0; cache[i1] = r1; }
         }
     }
     for (int d = rot + lane; d < width; d += 32) {
-        const TC r = from_f32<TC>(x[d] * inv);
+        const TC r = from_f32<TC>(w ? x[d] * inv * w[d] : x[d] * inv);
         if (dst) dst[d] = r;
         if (cache) cache[d] = r;
     }
@@ -102,13 +115,15 @@ TQ_API int tq_head_encode(const float* proj, int ld, int q_col, int k_col, int v
                           const float* sin_tab, int rot, float norm_eps, const int* tok_pos, const int* tok_seq,
                           const int* new_lens, const int* block_table, int table_width, int ring_pages,
                           int page_tokens, void* q_out, void* k_out, void* v_out, void* k_pages, void* v_pages,
-                          int cache_dtype, int n_tokens, int nh, int nkv, int hd, int vd, cudaStream_t stream) {
+                          int cache_dtype, int n_tokens, int nh, int nkv, int hd, int vd, const float* row_inv,
+                          const float* q_w, const float* k_w, int paired, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (row_inv && (!q_w || (nkv > 0 && !k_w) || norm_eps > 0.f)) return (int)cudaErrorInvalidValue;
     if (rot < 0 || rot > hd || (rot & 1) || page_tokens <= 0 || hd <= 0 || vd <= 0) return (int)cudaErrorInvalidValue;
     if (rot > 0 && (!cos_tab || !sin_tab)) return (int)cudaErrorInvalidValue;
     if ((k_pages == nullptr) != (v_pages == nullptr)) return (int)cudaErrorInvalidValue;
     if (k_pages && !block_table) return (int)cudaErrorInvalidValue;
-    if (v_col < 0 && vd != hd) return (int)cudaErrorInvalidValue;
+    if (nkv > 0 && v_col < 0 && vd != hd) return (int)cudaErrorInvalidValue;
     const int groups = (nh + 2 * nkv + 3) / 4;
     if (groups > 65535) return (int)cudaErrorInvalidValue;
     const dim3 grid(n_tokens, groups);
@@ -116,11 +131,43 @@ TQ_API int tq_head_encode(const float* proj, int ld, int q_col, int k_col, int v
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, head_encode_kernel<TC>, grid, dim3(128), 0, stream, proj, ld, q_col,  \
                          k_col, v_col, cos_tab, sin_tab, rot, norm_eps, tok_pos, tok_seq, new_lens, block_table,   \
                          table_width, ring_pages, page_tokens, (TC*)q_out, (TC*)k_out, (TC*)v_out, (TC*)k_pages,   \
-                         (TC*)v_pages, nh, nkv, hd, vd)
+                         (TC*)v_pages, nh, nkv, hd, vd, row_inv, q_w, k_w, paired)
     if (cache_dtype == TQ_F32) TQ_LAUNCH(float);
     if (cache_dtype == TQ_BF16) TQ_LAUNCH(bf16);
 #undef TQ_LAUNCH
     return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// out[t, 0] = 1 / sqrt(sum(q row^2) / q_count + eps), out[t, 1] likewise for the k row (k_n == 0: no k row): the
+// factors of an RMS norm over a token's whole q and k projections.  The counts are the rows' true lengths where
+// the rows are padded with zeros.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+row_inv_rms_kernel(const float* __restrict__ proj, int ld, int q_col, int q_n, int q_count, int k_col, int k_n,
+                   int k_count, float eps, float* __restrict__ out) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
+    const float* row = proj + (size_t)t * ld;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_n; i += blockDim.x) ss = fmaf(row[q_col + i], row[q_col + i], ss);
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) out[2 * t] = 1.f / sqrtf(ss / (float)q_count + eps);
+    if (k_n <= 0) return;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < k_n; i += blockDim.x) ss = fmaf(row[k_col + i], row[k_col + i], ss);
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) out[2 * t + 1] = 1.f / sqrtf(ss / (float)k_count + eps);
+}
+
+TQ_API int tq_row_inv_rms(const float* proj, int ld, int q_col, int q_n, int q_count, int k_col, int k_n, int k_count,
+                          float eps, float* out, int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!proj || !out || q_n <= 0 || q_count <= 0 || k_n < 0 || (k_n > 0 && k_count <= 0)) return (int)cudaErrorInvalidValue;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, row_inv_rms_kernel, dim3(n_tokens), dim3(q_n >= 1024 ? 256 : 128), 0, stream,
+                         proj, ld, q_col, q_n, q_count, k_col, k_n, k_count, eps, out);
 }
 
 // ---------------------------------------------------------------------------

@@ -43,7 +43,7 @@ __global__ void latent_rows_kernel(const float* __restrict__ proj, int ld, int o
                                    int paired, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                    const int* __restrict__ new_lens, T* __restrict__ cq_out, T* __restrict__ row_out,
                                    T* __restrict__ pages, const int* __restrict__ block_table, int table_width,
-                                   int page_tokens) {
+                                   int page_tokens, int ring_pages) {
     extern __shared__ float sh[];          // [r] the raw rotated part
     __shared__ float red[32];
     const int t = blockIdx.x;
@@ -51,13 +51,15 @@ __global__ void latent_rows_kernel(const float* __restrict__ proj, int ld, int o
     pdl_launch();
     const float* row = proj + (size_t)t * ld;
     const int pos = tok_pos[t], b = tok_seq[t];
-    // the query latent
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss = fmaf(row[off_q + i], row[off_q + i], ss);
-    ss = block_sum(ss, red);
-    float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
-        cq_out[(size_t)t * q_rank + i] = from_f32<T>(row[off_q + i] * inv * wq[i]);
+    // the query latent (q_rank == 0: the queries are projected directly and there is none)
+    float ss = 0.f, inv = 0.f;
+    if (q_rank > 0) {
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss = fmaf(row[off_q + i], row[off_q + i], ss);
+        ss = block_sum(ss, red);
+        inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+            cq_out[(size_t)t * q_rank + i] = from_f32<T>(row[off_q + i] * inv * wq[i]);
+    }
     // the cache row
     ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(row[off_kv + i], row[off_kv + i], ss);
@@ -66,8 +68,10 @@ __global__ void latent_rows_kernel(const float* __restrict__ proj, int ld, int o
     for (int i = threadIdx.x; i < r; i += blockDim.x) sh[i] = row[off_kv + n + i];
     __syncthreads();
     T* dst_page = nullptr;
-    if (pages && pos < new_lens[b]) {
-        const int page = block_table[(size_t)b * table_width + pos / page_tokens];
+    // in a ring (a window's cache) only the last ring_pages * page_tokens positions of a sequence are written
+    if (pages && pos < new_lens[b] && (ring_pages <= 0 || pos >= new_lens[b] - ring_pages * page_tokens)) {
+        const int lp = ring_pages > 0 ? (pos / page_tokens) % ring_pages : pos / page_tokens;
+        const int page = block_table[(size_t)b * table_width + lp];
         dst_page = pages + ((size_t)page * page_tokens + (pos % page_tokens)) * rp;
     }
     T* dst_row = row_out ? row_out + (size_t)t * rp : nullptr;
@@ -84,7 +88,7 @@ __global__ void latent_rows_kernel(const float* __restrict__ proj, int ld, int o
 }
 
 template <typename T>
-__global__ void latent_query_kernel(const float* __restrict__ q, int H, int d, int r, int n, int rp,
+__global__ void latent_query_kernel(const float* __restrict__ q, int ldq, int H, int d, int r, int n, int rp,
                                     const T* __restrict__ uk, const float* __restrict__ cos_t,
                                     const float* __restrict__ sin_t, int rot_dims, int paired,
                                     const int* __restrict__ tok_pos, T* __restrict__ out) {
@@ -92,7 +96,7 @@ __global__ void latent_query_kernel(const float* __restrict__ q, int H, int d, i
     const int t = blockIdx.x, h = blockIdx.y;
     pdl_wait();
     pdl_launch();
-    const float* qr = q + ((size_t)t * H + h) * (d + r);
+    const float* qr = q + (size_t)t * ldq + (size_t)h * (d + r);
     for (int i = threadIdx.x; i < d + r; i += blockDim.x) sh[i] = qr[i];
     __syncthreads();
     const int pos = tok_pos[t];
@@ -114,7 +118,7 @@ __global__ void latent_query_kernel(const float* __restrict__ q, int H, int d, i
 // q float32 [T, H * (d + r)]; kfv float32 [T, ldk]: head h's flat key at column h * d, its value at off_v + h * e;
 // rows [T, rp]: the cache rows, whose entries n .. n + r - 1 are the rotated key part.
 template <typename T>
-__global__ void latent_heads_kernel(const float* __restrict__ q, const float* __restrict__ kfv, int ldk, int off_v,
+__global__ void latent_heads_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ kfv, int ldk, int off_v,
                                     const T* __restrict__ rows, int rp, int n, int H, int d, int r, int e, int hw,
                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
                                     int paired, const int* __restrict__ tok_pos, T* __restrict__ q_out,
@@ -123,7 +127,7 @@ __global__ void latent_heads_kernel(const float* __restrict__ q, const float* __
     const int t = blockIdx.x, h = blockIdx.y;
     pdl_wait();
     pdl_launch();
-    const float* qr = q + ((size_t)t * H + h) * (d + r);
+    const float* qr = q + (size_t)t * ldq + (size_t)h * (d + r);
     for (int i = threadIdx.x; i < r; i += blockDim.x) sh[i] = qr[d + i];
     __syncthreads();
     const int pos = tok_pos[t];
@@ -180,9 +184,10 @@ TQ_API int tq_latent_rows(const float* proj, int ld, int off_q, int off_kv, int 
                           const float* wq, const float* wkv, float eps, const float* cos_t, const float* sin_t,
                           int rot_dims, int paired, const int* tok_pos, const int* tok_seq, const int* new_lens,
                           void* cq_out, void* row_out, void* pages, const int* block_table, int table_width,
-                          int page_tokens, int dtype, int n_tokens, cudaStream_t stream) {
+                          int page_tokens, int ring_pages, int dtype, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (!proj || !wq || !wkv || !cos_t || !sin_t || !tok_pos || !tok_seq || !new_lens || !cq_out || q_rank <= 0 || n <= 0 ||
+    if (!proj || !wkv || !cos_t || !sin_t || !tok_pos || !tok_seq || !new_lens || q_rank < 0 ||
+        (q_rank > 0 && (!wq || !cq_out)) || n <= 0 ||
         r < 0 || rp < n + r || rot_dims < 0 || rot_dims > r || (rot_dims & 1) || (pages && (!block_table || page_tokens <= 0)))
         return (int)cudaErrorInvalidValue;
     const int threads = (n >= 512 || q_rank >= 512) ? 256 : 128;
@@ -191,16 +196,16 @@ TQ_API int tq_latent_rows(const float* proj, int ld, int off_q, int off_kv, int 
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_rows_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
                              proj, ld, off_q, off_kv, q_rank, n, r, rp, wq, wkv, eps, cos_t, sin_t, rot_dims, paired,
                              tok_pos, tok_seq, new_lens, (float*)cq_out, (float*)row_out, (float*)pages, block_table,
-                             table_width, page_tokens);
+                             table_width, page_tokens, ring_pages);
     if (dtype == TQ_BF16)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, stream,
                              proj, ld, off_q, off_kv, q_rank, n, r, rp, wq, wkv, eps, cos_t, sin_t, rot_dims, paired,
                              tok_pos, tok_seq, new_lens, (bf16*)cq_out, (bf16*)row_out, (bf16*)pages, block_table,
-                             table_width, page_tokens);
+                             table_width, page_tokens, ring_pages);
     return (int)cudaErrorInvalidValue;
 }
 
-TQ_API int tq_latent_query(const float* q, int H, int d, int r, int n, int rp, const void* uk, const float* cos_t,
+TQ_API int tq_latent_query(const float* q, int ldq, int H, int d, int r, int n, int rp, const void* uk, const float* cos_t,
                            const float* sin_t, int rot_dims, int paired, const int* tok_pos, void* out, int dtype,
                            int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -211,10 +216,10 @@ TQ_API int tq_latent_query(const float* q, int H, int d, int r, int n, int rp, c
     const size_t smem = (size_t)(d + r) * sizeof(float);
     const dim3 grid(n_tokens, H);
     if (dtype == TQ_F32)
-        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_query_kernel<float>, grid, dim3(threads), smem, stream, q, H, d, r,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_query_kernel<float>, grid, dim3(threads), smem, stream, q, ldq, H, d, r,
                              n, rp, (const float*)uk, cos_t, sin_t, rot_dims, paired, tok_pos, (float*)out);
     if (dtype == TQ_BF16)
-        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_query_kernel<bf16>, grid, dim3(threads), smem, stream, q, H, d, r,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_query_kernel<bf16>, grid, dim3(threads), smem, stream, q, ldq, H, d, r,
                              n, rp, (const bf16*)uk, cos_t, sin_t, rot_dims, paired, tok_pos, (bf16*)out);
     return (int)cudaErrorInvalidValue;
 }
@@ -234,7 +239,7 @@ TQ_API int tq_latent_expand(const void* lat, int H, int n, int rp, int e, const 
     return (int)cudaErrorInvalidValue;
 }
 
-TQ_API int tq_latent_heads(const float* q, const float* kfv, int ldk, int off_v, const void* rows, int rp, int n, int H,
+TQ_API int tq_latent_heads(const float* q, int ldq, const float* kfv, int ldk, int off_v, const void* rows, int rp, int n, int H,
                            int d, int r, int e, int hw, const float* cos_t, const float* sin_t, int rot_dims, int paired,
                            const int* tok_pos, void* q_out, void* k_out, void* v_out, int dtype, int n_tokens,
                            cudaStream_t stream) {
@@ -245,11 +250,11 @@ TQ_API int tq_latent_heads(const float* q, const float* kfv, int ldk, int off_v,
     const dim3 grid(n_tokens, H);
     const size_t smem = (size_t)(r > 0 ? r : 1) * sizeof(float);
     if (dtype == TQ_F32)
-        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<float>, grid, dim3(128), smem, stream, q, kfv, ldk,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<float>, grid, dim3(128), smem, stream, q, ldq, kfv, ldk,
                              off_v, (const float*)rows, rp, n, H, d, r, e, hw, cos_t, sin_t, rot_dims, paired, tok_pos,
                              (float*)q_out, (float*)k_out, (float*)v_out);
     if (dtype == TQ_BF16)
-        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<bf16>, grid, dim3(128), smem, stream, q, kfv, ldk,
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<bf16>, grid, dim3(128), smem, stream, q, ldq, kfv, ldk,
                              off_v, (const bf16*)rows, rp, n, H, d, r, e, hw, cos_t, sin_t, rot_dims, paired, tok_pos,
                              (bf16*)q_out, (bf16*)k_out, (bf16*)v_out);
     return (int)cudaErrorInvalidValue;

@@ -1,6 +1,7 @@
 // A feed-forward of many small experts of which each token uses a few, named by
 // a table (or any int32 list): expert e is  W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),
-// and a token's result is the mean of its experts' results.
+// and a token's result is the mean of its experts' results, or their sum with a weight per (token, expert)
+// where a router gives weights (router_choice below).
 //
 // The experts' weights are stacked: w_gu [E, 2*F, W] (an expert's gate rows, then its up rows) and
 // w_down [E, W, F].  choice [T, top] int32 names each token's experts.
@@ -34,6 +35,49 @@ TQ_API int tq_table_choice(const int* tokens, const int* table, int vocab, int t
     if (n <= 0) return 0;
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, table_choice_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens,
                          table, vocab, top, n_experts, choice, n);
+}
+
+// ---- choice: experts of each token from a router's logits -------------------------------------------------------
+// scores s = sigmoid(logit); the `top` largest are chosen (the lowest index first among equals); their weights
+// are  scale * s / (sum of the chosen s + floor).  A warp per token; float32 throughout.
+__global__ void __launch_bounds__(128)
+router_choice_kernel(const float* __restrict__ logits, int ld, int n_experts, int top, float scale, float floor_,
+                     int* __restrict__ choice, float* __restrict__ weights, int n_tokens) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n_tokens) return;
+    pdl_wait();
+    pdl_launch();
+    const float* z = logits + (size_t)t * ld;
+    float total = 0.f;
+    for (int s = 0; s < top; ++s) {
+        float best = -1.f;
+        int best_e = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            bool taken = false;
+            for (int r = 0; r < s; ++r) taken |= choice[t * top + r] == e;
+            const float v = 1.f / (1.f + expf(-z[e]));
+            if (!taken && v > best) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (lane == 0) { choice[t * top + s] = best_e; weights[t * top + s] = best; }
+        __syncwarp();
+        total += best;
+    }
+    const float f = scale / (total + floor_);
+    for (int s = lane; s < top; s += 32) weights[t * top + s] *= f;
+}
+
+TQ_API int tq_router_choice(const float* logits, int ld, int n_experts, int top, float scale, float floor_, int* choice,
+                            float* weights, int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!logits || !choice || !weights || top < 1 || top > n_experts) return (int)cudaErrorInvalidValue;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, router_choice_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits,
+                         ld, n_experts, top, scale, floor_, choice, weights, n_tokens);
 }
 
 // ---- a warp's inner product over n entries ---------------------------------------------------------------------
@@ -78,8 +122,9 @@ routed_gate_up_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ 
 // grid (T, ceil(W / 8)), 8 warps: warp w computes column c = blockIdx.y*8 + w
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
-routed_down_kernel(const TA* __restrict__ act, const TW* __restrict__ w_down, const int* __restrict__ choice, int top,
-                   int W, int F, float* __restrict__ y, int accumulate, bool vec) {
+routed_down_kernel(const TA* __restrict__ act, const TW* __restrict__ w_down, const int* __restrict__ choice,
+                   const float* __restrict__ weights, int top, int W, int F, float* __restrict__ y, int accumulate,
+                   bool vec) {
     const int t = blockIdx.x;
     const int c = blockIdx.y * 8 + (threadIdx.x >> 5);
     if (c >= W) return;
@@ -88,11 +133,12 @@ routed_down_kernel(const TA* __restrict__ act, const TW* __restrict__ w_down, co
     float sum = 0.f;
     for (int s = 0; s < top; ++s) {
         const int e = choice[t * top + s];
-        sum += warp_dot<TA, TW>(act + (size_t)(t * top + s) * F, w_down + ((size_t)e * W + c) * F, F, vec);
+        const float part = warp_dot<TA, TW>(act + (size_t)(t * top + s) * F, w_down + ((size_t)e * W + c) * F, F, vec);
+        sum = weights ? fmaf(weights[t * top + s], part, sum) : sum + part;
     }
     if ((threadIdx.x & 31) == 0) {
         float* o = y + (size_t)t * W + c;
-        const float v = sum / (float)top;
+        const float v = weights ? sum : sum / (float)top;
         *o = accumulate ? *o + v : v;
     }
 }
@@ -101,8 +147,8 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 // x [T, W] (row stride ldx), act [T*top, F] of x's dtype (scratch), y [T, W] float32.  Weights float32 or bfloat16.
 TQ_API int tq_routed_experts_rows(const void* x, int x_dtype, int ldx, const void* w_gu, const void* w_down, int w_dtype,
-                                  const int* choice, int top, int n_tokens, int W, int F, void* act, float* y,
-                                  int accumulate, cudaStream_t stream) {
+                                  const int* choice, const float* weights, int top, int n_tokens, int W, int F,
+                                  void* act, float* y, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || W <= 0 || F <= 0) return (int)cudaErrorInvalidValue;
     const int xs = x_dtype == TQ_BF16 ? 2 : 4, ws = w_dtype == TQ_BF16 ? 2 : 4;
@@ -117,7 +163,7 @@ TQ_API int tq_routed_experts_rows(const void* x, int x_dtype, int ldx, const voi
                        ldx, (const TW*)w_gu, choice, top, W, F, (TX*)act, vec_up);                                   \
     if (st) return st;                                                                                                \
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, routed_down_kernel<TX, TW>, g2, dim3(256), 0, stream, (const TX*)act,   \
-                         (const TW*)w_down, choice, top, W, F, y, accumulate, vec_down)
+                         (const TW*)w_down, choice, weights, top, W, F, y, accumulate, vec_down)
     if (x_dtype == TQ_F32 && w_dtype == TQ_F32) { TQ_RUN(float, float); }
     if (x_dtype == TQ_F32 && w_dtype == TQ_BF16) { TQ_RUN(float, bf16); }
     if (x_dtype == TQ_BF16 && w_dtype == TQ_BF16) { TQ_RUN(bf16, bf16); }
@@ -178,19 +224,20 @@ routed_gather_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict_
 
 // y[t] (=, +=) 1/top * sum_s out[pos[t*top + s]] (the experts in the table's order): float32, W % 4 == 0
 __global__ void __launch_bounds__(256)
-routed_combine_kernel(const float* __restrict__ out, const int* __restrict__ pos, int top, int W, int n_tokens,
-                      float* __restrict__ y, int accumulate) {
+routed_combine_kernel(const float* __restrict__ out, const int* __restrict__ pos, const float* __restrict__ weights,
+                      int top, int W, int n_tokens, float* __restrict__ y, int accumulate) {
     pdl_wait();
     pdl_launch();
     const int per_row = W / 4;
-    const float inv = 1.f / (float)top;
+    const float inv = weights ? 1.f : 1.f / (float)top;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)n_tokens * per_row;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / per_row), c = (int)(idx - (size_t)t * per_row);
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int s = 0; s < top; ++s) {
             const float4 v = reinterpret_cast<const float4*>(out + (size_t)pos[t * top + s] * W)[c];
-            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+            const float ws = weights ? weights[t * top + s] : 1.f;
+            a.x = fmaf(ws, v.x, a.x); a.y = fmaf(ws, v.y, a.y); a.z = fmaf(ws, v.z, a.z); a.w = fmaf(ws, v.w, a.w);
         }
         float4* o = reinterpret_cast<float4*>(y + (size_t)t * W) + c;
         if (accumulate) {
@@ -220,12 +267,12 @@ TQ_API int tq_routed_sort(const void* x, int ldx, const int* choice, int top, in
                          (const bf16*)x, ldx, (const int*)pos, top, W, n_pairs, (bf16*)sorted);
 }
 
-TQ_API int tq_routed_combine(const float* out, const int* pos, int top, int n_tokens, int W, float* y, int accumulate,
-                             cudaStream_t stream) {
+TQ_API int tq_routed_combine(const float* out, const int* pos, const float* weights, int top, int n_tokens, int W,
+                             float* y, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (W % 4 || !aligned16(out) || !aligned16(y)) return (int)cudaErrorInvalidValue;
     size_t blocks = ((size_t)n_tokens * (W / 4) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, routed_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, out, pos,
-                         top, W, n_tokens, y, accumulate);
+                         weights, top, W, n_tokens, y, accumulate);
 }

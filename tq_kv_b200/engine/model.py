@@ -114,9 +114,10 @@ class DecoderModel:
         if self.spec.residual_streams > 0:
             h = ResidualStreams(h, self.spec.residual_streams)
         kernels.mark("embed")
+        step_shared: dict = {}
         for i, e in enumerate(self.spec.schedule):
             owner = i if e.cache_of is None else e.cache_of
-            ctx = StepContext(batch=batch, runtime=rt, entry=i)
+            ctx = StepContext(batch=batch, runtime=rt, entry=i, cache_entry=owner, step_shared=step_shared)
             if owner in cache.group_of_entry:
                 gi, k_pages, v_pages = cache.layer_pages(owner)
                 table, width = batch.block_tables[gi]

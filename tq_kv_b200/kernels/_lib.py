@@ -146,7 +146,7 @@ _SIGNATURES = {
     "tq_qkv_rope_cache": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "tq_swiglu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tq_swiglu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tq_add_into": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
     "tq_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
@@ -174,7 +174,7 @@ _SIGNATURES = {
     "tq_flash_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int,
                             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int,
                             c_void_p, c_void_p],
-    "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_embed_sinusoid": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "tq_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
                          c_float, c_int, c_void_p],
@@ -187,10 +187,10 @@ _SIGNATURES = {
                       c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "tq_latent_rows": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
                        c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_int, c_void_p],
-    "tq_latent_query": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_latent_query": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_int, c_int, c_void_p],
-    "tq_latent_heads": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "tq_latent_heads": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "tq_latent_expand": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                          c_void_p],
@@ -215,30 +215,38 @@ _SIGNATURES = {
     "tq_sigmoid_attention_sum": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_attention_ext": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
-                         c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
+                         c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "tq_flash_prefill_tc_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int,
                                 c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
-                                c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+                                c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "tq_flash_prefill_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                             c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_int, c_void_p,
                              c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "tq_flash_decode_ext": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                            c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_float, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_int, c_void_p],
     "tq_head_encode": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "tq_row_inv_rms": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "tq_add_normed_copy": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "tq_round_rows": [c_void_p, c_void_p, c_size_t, c_void_p],
+    "tq_router_choice": [c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p],
+    "tq_mlstm_gates": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int,
+                       c_void_p, c_int, c_void_p],
+    "tq_mlstm_read": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_float, c_int,
+                      c_void_p, c_int, c_int, c_void_p],
     "tq_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "tq_tanh_cap": [c_void_p, c_size_t, c_float, c_void_p],
     "tq_streams_step": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                         c_void_p, c_int, c_void_p, c_int, c_void_p],
     "tq_streams_fill": [c_void_p, c_void_p, c_int, c_size_t, c_void_p],
     "tq_table_choice": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
-    "tq_routed_experts_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                               c_void_p, c_void_p, c_int, c_void_p],
+    "tq_routed_experts_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_void_p, c_void_p, c_int, c_void_p],
     "tq_routed_sort": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_void_p],
-    "tq_routed_combine": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "tq_routed_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "tq_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_int, c_void_p, c_void_p, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,

@@ -107,7 +107,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_heads: i
             check(st, "flash_decode")
             if n_splits > 1:
                 check(core().tq_attention_merge(ptr(part_acc), ptr(part_ml), ptr(out), dtype_code(out), T, n_heads,
-                                                head_dim, n_splits, stream()), "attention_merge")
+                                                head_dim, n_splits, 0, stream()), "attention_merge")
             return out
     check(core().tq_attention(
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
@@ -134,13 +134,14 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
                   k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                   block_table: Optional[torch.Tensor] = None, table_width: int = 0, ring_pages: int = 0,
                   page_tokens: int = 64, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                  gate: Optional[torch.Tensor] = None, use_fast: bool = True):
+                  gate: Optional[torch.Tensor] = None, use_fast: bool = True, sink: bool = False):
     """Softmax attention with options: for the query at position i of head h and the key at position j <= i,
 
         s = q . k * scale;   s <- softcap * tanh(s / softcap)  (if a cap is given);
         s <- s - slopes[h] * (i - j)                            (if slopes are given);
 
-    j is visible if i - j < window or j < keep_first (no window: every j <= i).  Value rows may have another
+    j is visible if i - j < window or j < keep_first (no window: every j <= i).  With `sink` the softmax's
+    denominator counts one more key of score 0 that has no value: p_j = exp(s_j) / (1 + sum exp(s)).  Value rows may have another
     width than the keys.  q [T, nh*key_dim], out [T, nh*value_dim]; keys and values as in `attention`.
     `gate` (float32 [T, nh*value_dim], possibly a column slice of wider rows): out *= sigmoid(gate), in the
     attention kernel's last step where it can, else by a kernel of its own.
@@ -191,7 +192,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
                 ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages),
                 0 if k_pages is None else k_pages.shape[0], ptr(block_table), table_width, ring_pages, page_tokens,
                 ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale), float(softcap or 0.0),
-                ptr(slopes), keep, g_ptr, g_ld, ptr(out), n_heads, n_kv_heads, key_dim,
+                ptr(slopes), keep, int(sink), g_ptr, g_ld, ptr(out), n_heads, n_kv_heads, key_dim,
                 ptr(tc_status_word(q.device)), stream())
             if st != NOT_SUPPORTED:
                 check(st, "flash_prefill_tc_ext")
@@ -199,8 +200,8 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
             st = core().tq_flash_prefill_ext(
                 ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width,
                 ring_pages, page_tokens, ptr(cu_seqlens), ptr(start_pos), n_seqs, T, int(window or 0), float(scale),
-                float(softcap or 0.0), ptr(slopes), keep, g_ptr, g_ld, ptr(out), n_heads, n_kv_heads, key_dim,
-                stream())
+                float(softcap or 0.0), ptr(slopes), keep, int(sink), g_ptr, g_ld, ptr(out), n_heads, n_kv_heads,
+                key_dim, stream())
             if st != NOT_SUPPORTED:
                 check(st, "flash_prefill_ext")
         if st != NOT_SUPPORTED:
@@ -211,13 +212,13 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
     if fast and not packed:
         st = core().tq_flash_decode_ext(
             ptr(q), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width, ring_pages, page_tokens, ptr(tok_pos),
-            ptr(tok_seq), int(window or 0), float(scale), float(softcap or 0.0), ptr(slopes), keep, ptr(out),
-            ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim, n_splits, stream())
+            ptr(tok_seq), int(window or 0), float(scale), float(softcap or 0.0), ptr(slopes), keep, int(sink),
+            ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim, n_splits, stream())
         if st != NOT_SUPPORTED:
             check(st, "flash_decode_ext")
             if n_splits > 1:
                 check(core().tq_attention_merge(ptr(part_acc), ptr(part_ml), ptr(out), dtype_code(out), T, n_heads,
-                                                value_dim, n_splits, stream()), "attention_merge")
+                                                value_dim, n_splits, int(sink), stream()), "attention_merge")
             if gate is not None:
                 from .elementwise import sigmoid_gate
                 sigmoid_gate(out, gate)
@@ -226,7 +227,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_head
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table),
         table_width, ring_pages, page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos),
         int(window or 0), float(scale), ptr(out), ptr(part_acc), ptr(part_ml), T, n_heads, n_kv_heads, key_dim,
-        value_dim, float(softcap or 0.0), ptr(slopes), keep, n_splits, stream()),
+        value_dim, float(softcap or 0.0), ptr(slopes), keep, int(sink), n_splits, stream()),
         "attention_ext", 2 if n_splits > 1 else 1)
     if gate is not None:
         from .elementwise import sigmoid_gate

@@ -70,14 +70,25 @@ def qkv_rope_cache(qkv, bias, cos, sin, tok_pos, tok_seq, new_lens, q_out, *, n_
         "qkv_rope_cache")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor):
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
-    T, two_i = gate_up.shape
-    I = two_i // 2
-    if two_i != 2 * I or tuple(out.shape) != (T, I):
+ACT_SILU, ACT_GELU_TANH = 1, 2          # the gate's activation in a gated feed-forward (csrc/common.cuh)
+
+
+def activation_code(name: str) -> int:
+    try:
+        return {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}[name]
+    except KeyError:
+        raise KernelError(f"unknown gate activation '{name}' (silu, gelu_tanh)") from None
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, act: int = ACT_SILU):
+    """out = act(gate) * up for gate_up [T, 2I] = [gate | up]; act: silu (the default) or the tanh form of gelu."""
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    if I2 % 2 or tuple(out.shape) != (T, I):
         raise KernelError("swiglu: gate_up must be [T, 2I] and out [T, I]")
     need_contiguous(gate_up=gate_up, out=out)
-    check(core().tq_swiglu(ptr(gate_up), dtype_code(gate_up), ptr(out), dtype_code(out), T, I, stream()), "swiglu")
+    check(core().tq_swiglu(ptr(gate_up), dtype_code(gate_up), ptr(out), dtype_code(out), T, I, int(act), stream()),
+          "swiglu")
     return out
 
 
@@ -213,12 +224,15 @@ def scale_inplace(x: torch.Tensor, s: float):
 def head_encode(proj: torch.Tensor, ctx_pos, q_out: torch.Tensor, *, q_col: int, k_col: int, v_col: int,
                 n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, cos=None, sin=None, rotary_dim: int = 0,
                 norm_eps: float = 0.0, k_out=None, v_out=None, k_pages=None, v_pages=None, block_table=None,
-                table_width: int = 0, ring_pages: int = 0, page_tokens: int = 64):
+                table_width: int = 0, ring_pages: int = 0, page_tokens: int = 64, paired: bool = False,
+                row_inv=None, q_weight=None, k_weight=None):
     """From projected float32 rows [T, ld] (q heads from column q_col, k heads from k_col, v heads from v_col; with
     v_col < 0 the values are the keys as projected) to encoded q, and k / v packed and / or appended to the cache
     (see csrc/head_encode.cu).  `ctx_pos` = (tok_pos, tok_seq, new_lens).  q and k are rotated over their first
-    `rotary_dim` entries (cos/sin float32 [positions, rotary_dim/2]) or, with norm_eps > 0, divided by their root
-    mean square per head."""
+    `rotary_dim` entries (cos/sin float32 [positions, rotary_dim/2]; entry i with i + rotary_dim/2, or with
+    `paired` entry 2i with 2i + 1) or, with norm_eps > 0, divided by their root mean square per head.  With
+    `row_inv` (float32 [T, 2] from `row_inv_rms`) and the weights q_weight [n_heads * key_dim] and k_weight
+    [n_kv_heads * key_dim], q and k are first normed over their whole rows.  n_kv_heads may be 0: only q is encoded."""
     tok_pos, tok_seq, new_lens = ctx_pos
     T, ld = proj.shape
     if proj.dtype != torch.float32 or proj.stride(1) != 1:
@@ -227,7 +241,7 @@ def head_encode(proj: torch.Tensor, ctx_pos, q_out: torch.Tensor, *, q_col: int,
         if rotary_dim % 2 or rotary_dim > key_dim or cos is None or cos.dtype != torch.float32 \
                 or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape:
             raise KernelError(f"head_encode: rotary_dim {rotary_dim} needs float32 tables [positions, {rotary_dim // 2}]")
-    if v_col < 0 and value_dim != key_dim:
+    if n_kv_heads and v_col < 0 and value_dim != key_dim:
         raise KernelError("head_encode: values that are the keys have the keys' width")
     need = max(q_col + n_heads * key_dim, k_col + n_kv_heads * key_dim, v_col + n_kv_heads * value_dim if v_col >= 0 else 0)
     if need > ld or min(q_col, k_col) < 0:
@@ -235,14 +249,61 @@ def head_encode(proj: torch.Tensor, ctx_pos, q_out: torch.Tensor, *, q_col: int,
     for t in (k_out, v_out, k_pages, v_pages):
         if t is not None and t.dtype != q_out.dtype:
             raise KernelError("head_encode: all outputs and the cache must share one dtype")
+    if row_inv is not None:
+        if (row_inv.dtype != torch.float32 or tuple(row_inv.shape) != (T, 2) or q_weight is None
+                or q_weight.dtype != torch.float32 or q_weight.shape[0] != n_heads * key_dim
+                or (n_kv_heads and (k_weight is None or k_weight.dtype != torch.float32
+                                    or k_weight.shape[0] != n_kv_heads * key_dim))):
+            raise KernelError("head_encode: row_inv float32 [T, 2] needs float32 weights over the whole q and k rows")
+        need_contiguous(row_inv=row_inv, q_weight=q_weight, k_weight=k_weight)
     need_contiguous(q_out=q_out, k_out=k_out, v_out=v_out, k_pages=k_pages, v_pages=v_pages, block_table=block_table,
                     cos=cos, sin=sin)
     check(core().tq_head_encode(ptr(proj), proj.stride(0), q_col, k_col, v_col, ptr(cos), ptr(sin), rotary_dim,
                                 float(norm_eps), ptr(tok_pos), ptr(tok_seq), ptr(new_lens), ptr(block_table),
                                 table_width, ring_pages, page_tokens, ptr(q_out), ptr(k_out), ptr(v_out), ptr(k_pages),
-                                ptr(v_pages), dtype_code(q_out), T, n_heads, n_kv_heads, key_dim, value_dim, stream()),
+                                ptr(v_pages), dtype_code(q_out), T, n_heads, n_kv_heads, key_dim, value_dim,
+                                ptr(row_inv), ptr(q_weight), ptr(k_weight), int(bool(paired)), stream()),
           "head_encode")
     return q_out
+
+
+def row_inv_rms(proj: torch.Tensor, *, q_col: int, q_width: int, q_count: int, k_col: int = 0, k_width: int = 0,
+                k_count: int = 0, eps: float) -> torch.Tensor:
+    """float32 [T, 2]: per token 1 / sqrt(sum(q row^2) / q_count + eps) over columns q_col .. q_col + q_width of
+    the float32 rows `proj`, and the same for the k row (k_width 0: there is none).  The counts are the rows' true
+    lengths where they are padded with zeros."""
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or q_col + q_width > ld or k_col + k_width > ld:
+        raise KernelError("row_inv_rms: float32 rows that hold both projections")
+    out = torch.empty((T, 2), dtype=torch.float32, device=proj.device)
+    check(core().tq_row_inv_rms(ptr(proj), proj.stride(0), q_col, q_width, q_count, k_col, k_width, k_count,
+                                float(eps), ptr(out), T, stream()), "row_inv_rms")
+    return out
+
+
+def add_normed_copy(acc: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                    copy: Optional[torch.Tensor] = None):
+    """acc[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight, and `copy` (bfloat16 or float32 [T, W], if given)
+    receives the new acc rounded to its type.  acc, y float32 [T, W] contiguous; weight float32 [W]."""
+    T, W = acc.shape
+    if acc.dtype != torch.float32 or y.dtype != torch.float32 or tuple(y.shape) != (T, W) \
+            or weight.dtype != torch.float32 or weight.shape[0] != W:
+        raise KernelError("add_normed_copy: acc and y float32 [T, W], weight float32 [W]")
+    if copy is not None and tuple(copy.shape) != (T, W):
+        raise KernelError("add_normed_copy: the copy must be [T, W]")
+    need_contiguous(acc=acc, y=y, weight=weight, copy=copy)
+    check(core().tq_add_normed_copy(ptr(acc), ptr(y), ptr(weight), T, W, float(eps), ptr(copy),
+                                    0 if copy is None else dtype_code(copy), stream()), "add_normed_copy")
+    return acc
+
+
+def round_rows(x: torch.Tensor) -> torch.Tensor:
+    """The float32 tensor x rounded to bfloat16."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("round_rows: x must be contiguous float32")
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    check(core().tq_round_rows(ptr(x), ptr(out), x.numel(), stream()), "round_rows")
+    return out
 
 
 def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor):

@@ -1,6 +1,8 @@
 """Python entry points of the routed feed-forward (csrc/routed_experts.cu)."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
@@ -18,9 +20,30 @@ def table_choice(tokens: torch.Tensor, table: torch.Tensor, n_experts: int) -> t
     return choice
 
 
+def router_choice(logits: torch.Tensor, top: int, scale: float, floor: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """From a router's float32 logits [T, E]: the `top` experts with the largest sigmoid(logit) per token
+    (int32 [T, top], the lowest index first among equals) and their weights scale * s / (sum of the chosen s +
+    floor) (float32 [T, top])."""
+    T, E = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or not 1 <= top <= E:
+        raise KernelError("router_choice: float32 logits [T, E], 1 <= top <= E")
+    choice = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    check(core().tq_router_choice(ptr(logits), logits.stride(0), E, top, float(scale), float(floor), ptr(choice),
+                                  ptr(weights), T, stream()), "router_choice")
+    return choice, weights
+
+
+def _check_weights(weights, choice):
+    if weights is not None and (weights.dtype != torch.float32 or weights.shape != choice.shape
+                                or not weights.is_contiguous()):
+        raise KernelError("routed_experts: weights float32 of choice's shape")
+
+
 def routed_experts_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, choice: torch.Tensor,
-                        y: torch.Tensor, accumulate: bool) -> torch.Tensor:
-    """y (=, +=) mean over a token's experts e of  w_down[e] (silu(gate[e] x) * (up[e] x)), every (token, expert)
+                        y: torch.Tensor, accumulate: bool, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y (=, +=) mean over a token's experts e (with `weights` float32 [T, top]: the sum weighted by them) of
+    w_down[e] (silu(gate[e] x) * (up[e] x)), every (token, expert)
     pair a row-times-matrix product of its own.  x [T, W]; w_gate_up [E, 2F, W]; w_down [E, W, F];
     choice int32 [T, top]; y float32 [T, W]."""
     T, W = x.shape
@@ -33,10 +56,11 @@ def routed_experts_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.
     if x.stride(1) != 1:
         raise KernelError("routed_experts: x must be contiguous along its rows")
     need_contiguous(w_gate_up=w_gate_up, w_down=w_down, choice=choice, y=y)
+    _check_weights(weights, choice)
     top = choice.shape[1]
     act = torch.empty((T * top, F), dtype=x.dtype, device=x.device)
     check(core().tq_routed_experts_rows(ptr(x), dtype_code(x), x.stride(0), ptr(w_gate_up), ptr(w_down),
-                                        dtype_code(w_down), ptr(choice), top, T, W, F, ptr(act), ptr(y),
+                                        dtype_code(w_down), ptr(choice), ptr(weights), top, T, W, F, ptr(act), ptr(y),
                                         int(accumulate), stream()), "routed_experts_rows", 2)
     return y
 
@@ -53,7 +77,7 @@ def routed_tiles_ok(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tens
 
 
 def routed_experts_tiles(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, choice: torch.Tensor,
-                         y: torch.Tensor, accumulate: bool) -> torch.Tensor:
+                         y: torch.Tensor, accumulate: bool, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same result as `routed_experts_rows` for many rows: the (token, expert) pairs are sorted by expert
     into a buffer in which every expert owns whole tiles of 128 rows; two tensor-core products over the whole
     buffer follow, in which each tile multiplies with its own expert's matrices (the first gates, silu(g) * u,
@@ -66,6 +90,7 @@ def routed_experts_tiles(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch
     if choice.dtype != torch.int32 or choice.shape[0] != T or y.dtype != torch.float32 or tuple(y.shape) != (T, W):
         raise KernelError("routed_experts: choice int32 [T, top], y float32 [T, W]")
     need_contiguous(w_gate_up=w_gate_up, w_down=w_down, choice=choice, y=y)
+    _check_weights(weights, choice)
     top = choice.shape[1]
     n_pairs = T * top
     max_tiles = n_pairs // TILE_ROWS + E
@@ -84,5 +109,6 @@ def routed_experts_tiles(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch
                                  2, E * 2 * F, F, ptr(tile_up), status, stream()), "routed_gate_up")
     check(lib.tq_gemm_tc_grouped(ptr(act), ptr(w_down), ptr(out), dtype_code(out), rows, W, F, F, F, W,
                                  0, E * W, 0, ptr(tile_down), status, stream()), "routed_down")
-    check(lib.tq_routed_combine(ptr(out), ptr(pos), top, T, W, ptr(y), int(accumulate), stream()), "routed_combine")
+    check(lib.tq_routed_combine(ptr(out), ptr(pos), ptr(weights), top, T, W, ptr(y), int(accumulate), stream()),
+          "routed_combine")
     return y

@@ -206,20 +206,21 @@ def gemm_tiled(x, w, out, bias=None, accumulate=False):
     return out
 
 
-def gemv_rows(x, w, out, bias=None, accumulate=False, swiglu=False):
+def gemv_rows(x, w, out, bias=None, accumulate=False, swiglu=False, activation=elementwise.ACT_SILU):
     M, K = x.shape
     N = out.shape[1]
     check(core().tq_gemv_rows(ptr(x), dtype_code(x), ptr(w), dtype_code(w), ptr(bias), ptr(out), dtype_code(out),
-                              M, N, K, x.stride(0), w.stride(0), out.stride(0), int(accumulate), int(swiglu),
+                              M, N, K, x.stride(0), w.stride(0), out.stride(0), int(accumulate),
+                              int(activation) if swiglu else 0,
                               stream()), "gemv_rows")
     return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-           accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+           accumulate: bool = False, swiglu: bool = False, activation: int = elementwise.ACT_SILU) -> torch.Tensor:
     """y = x · w^T (+ bias); with `swiglu`, w holds gate rows then up rows and
-    y = silu(x · gate^T) * (x · up^T); with `accumulate`, `out` (float32) gets
+    y = act(x · gate^T) * (x · up^T), act being silu unless `activation` names another; with `accumulate`, `out` (float32) gets
     y added to it.  x [M, K], w [N, K] (or [2N, K]); float32 accumulation
     throughout."""
     pending = x if isinstance(x, PendingNorm) else None
@@ -243,10 +244,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
         raise KernelError("linear: bias must be float32 with one entry per weight row")
     if M == 0:
         return out
+    other_act = swiglu and activation != elementwise.ACT_SILU
     if pending is not None:
-        if _fused_norm(pending, w, out, bias, accumulate, swiglu):
+        if not other_act and _fused_norm(pending, w, out, bias, accumulate, swiglu):
             return out
         x = pending.materialize()
+    if other_act and not (M <= ROW_KERNEL_MAX_ROWS and (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16)):
+        # the tensor-core kernels gate with silu: another activation runs after a plain product
+        y = linear(x, w, bias=bias, out_dtype=torch.float32)
+        return elementwise.swiglu(y, out, activation)
 
     # decoding: the TMA-fed tcgen05 kernel or the mma.sync kernel (_tc_takes says which, where both can)
     if (USE_TCGEN05 and M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
@@ -257,7 +263,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if _skinny_ok(x, w):
         return skinny_gemm(x, w, out, bias, accumulate, swiglu)
     if M <= ROW_KERNEL_MAX_ROWS:
-        return gemv_rows(x, w, out, bias, accumulate, swiglu)
+        return gemv_rows(x, w, out, bias, accumulate, swiglu, activation)
 
     if _tc_ok(x, w, out, swiglu) and (not accumulate or out.dtype == torch.float32):
         return gemm_tc(x, w, out, bias, EPI_SWIGLU if swiglu else (EPI_ACCUM if accumulate else EPI_STORE))
@@ -277,5 +283,5 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
     if swiglu:
         y = torch.empty((M, rows_w), dtype=torch.float32, device=x.device)
         gemm_tiled(x, w, y, bias, False)
-        return elementwise.swiglu(y, out)
+        return elementwise.swiglu(y, out, activation)
     return gemm_tiled(x, w, out, bias, accumulate)

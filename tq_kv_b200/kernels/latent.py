@@ -16,34 +16,40 @@ def _check_tables(cos, sin, rot_dims, r):
         raise KernelError("latent attention: cos/sin must be float32 [positions, rot_dims / 2]")
 
 
-def latent_rows(proj: torch.Tensor, cq_out: torch.Tensor, *, off_q: int, off_kv: int, q_rank: int, kv_rank: int,
+def latent_rows(proj: torch.Tensor, cq_out: Optional[torch.Tensor], *, off_q: int, off_kv: int, q_rank: int, kv_rank: int,
                 rot_dim: int, row_width: int, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float,
                 cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, paired: bool, tok_pos, tok_seq, new_lens,
                 row_out: Optional[torch.Tensor] = None, pages: Optional[torch.Tensor] = None,
-                block_table: Optional[torch.Tensor] = None, table_width: int = 0, page_tokens: int = 64):
-    """From the float32 results of the down projections (proj [T, ld]: the query latent at column off_q, the
+                block_table: Optional[torch.Tensor] = None, table_width: int = 0, page_tokens: int = 64,
+                ring_pages: int = 0, out_dtype: Optional[torch.dtype] = None):
+    """(q_rank 0: no query latent, cq_out and q_weight None; `out_dtype` then names the rows' type.  ring_pages > 0:
+    the pages of a sequence are a ring, written at logical page (pos / page_tokens) % ring_pages.)
+    From the float32 results of the down projections (proj [T, ld]: the query latent at column off_q, the
     key/value latent and the rotated key part at off_kv): cq_out [T, q_rank] = rms_norm(query latent) * q_weight;
     the cache row [rms_norm(latent) * kv_weight, rotated key part, zeros up to row_width] into row_out
     [T, row_width] and / or the sequence's page (pages [n, 1, page_tokens, row_width])."""
     T = proj.shape[0]
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or max(off_q + q_rank, off_kv + kv_rank + rot_dim) > proj.shape[1]:
         raise KernelError("latent_rows: proj must be float32 rows that hold both down projections")
-    if tuple(cq_out.shape) != (T, q_rank) or row_width < kv_rank + rot_dim:
+    if (q_rank > 0 and (cq_out is None or tuple(cq_out.shape) != (T, q_rank))) or row_width < kv_rank + rot_dim:
         raise KernelError("latent_rows: cq_out must be [T, q_rank]; rows must hold the latent and the rotated part")
+    dtype = cq_out.dtype if q_rank > 0 else (out_dtype or next(t.dtype for t in (row_out, pages) if t is not None))
     for name, t in (("row_out", row_out), ("pages", pages)):
-        if t is not None and (t.dtype != cq_out.dtype or t.shape[-1] != row_width):
+        if t is not None and (t.dtype != dtype or t.shape[-1] != row_width):
             raise KernelError(f"latent_rows: {name} must have cq_out's dtype and rows of {row_width}")
     if pages is not None and (block_table is None or tuple(pages.shape[1:]) != (1, page_tokens, row_width)):
         raise KernelError("latent_rows: pages must be [n, 1, page_tokens, row_width] with a block table")
-    if q_weight.dtype != torch.float32 or kv_weight.dtype != torch.float32 or q_weight.shape[0] != q_rank \
-            or kv_weight.shape[0] != kv_rank:
+    if kv_weight.dtype != torch.float32 or kv_weight.shape[0] != kv_rank or (
+            q_rank > 0 and (q_weight is None or q_weight.dtype != torch.float32 or q_weight.shape[0] != q_rank)):
         raise KernelError("latent_rows: the norms' weights must be float32 [q_rank] and [kv_rank]")
     _check_tables(cos, sin, rot_dims, rot_dim)
     need_contiguous(cq_out=cq_out, row_out=row_out, pages=pages, cos=cos, sin=sin, q_weight=q_weight, kv_weight=kv_weight)
+    q_rank = int(q_rank)
     check(core().tq_latent_rows(ptr(proj), proj.stride(0), off_q, off_kv, q_rank, kv_rank, rot_dim, row_width,
                                 ptr(q_weight), ptr(kv_weight), float(eps), ptr(cos), ptr(sin), rot_dims, int(paired),
                                 ptr(tok_pos), ptr(tok_seq), ptr(new_lens), ptr(cq_out), ptr(row_out), ptr(pages),
-                                ptr(block_table), table_width, page_tokens, dtype_code(cq_out), T, stream()),
+                                ptr(block_table), table_width, page_tokens, int(ring_pages),
+                                dtype_code(torch.empty(0, dtype=dtype)), T, stream()),
           "latent_rows")
 
 
@@ -53,15 +59,15 @@ def latent_query(q: torch.Tensor, up_k: torch.Tensor, out: torch.Tensor, *, head
     space.  q float32 [T, heads * (dim + rot_dim)]; up_k [heads * dim, kv_rank] of out's dtype; out
     [T, heads * row_width]."""
     T = q.shape[0]
-    if q.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)):
-        raise KernelError("latent_query: q must be float32 [T, heads * (dim + rot_dim)]")
+    if q.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)) or q.stride(1) != 1:
+        raise KernelError("latent_query: q must be float32 [T, heads * (dim + rot_dim)] (may be a column slice)")
     if tuple(up_k.shape) != (heads * dim, kv_rank) or up_k.dtype != out.dtype:
         raise KernelError("latent_query: up_k must be [heads * dim, kv_rank] of out's dtype")
     if tuple(out.shape) != (T, heads * row_width) or row_width < kv_rank + rot_dim:
         raise KernelError("latent_query: out must be [T, heads * row_width]")
     _check_tables(cos, sin, rot_dims, rot_dim)
-    need_contiguous(q=q, up_k=up_k, out=out, cos=cos, sin=sin)
-    check(core().tq_latent_query(ptr(q), heads, dim, rot_dim, kv_rank, row_width, ptr(up_k), ptr(cos), ptr(sin),
+    need_contiguous(up_k=up_k, out=out, cos=cos, sin=sin)
+    check(core().tq_latent_query(ptr(q), q.stride(0), heads, dim, rot_dim, kv_rank, row_width, ptr(up_k), ptr(cos), ptr(sin),
                                  rot_dims, int(paired), ptr(tok_pos), ptr(out), dtype_code(out), T, stream()),
           "latent_query")
     return out
@@ -77,8 +83,8 @@ def latent_heads(q: torch.Tensor, kfv: torch.Tensor, rows: torch.Tensor, q_out: 
     dtype (the cache rows)."""
     T = q.shape[0]
     hw = q_out.shape[1] // heads
-    if q.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)):
-        raise KernelError("latent_heads: q must be float32 [T, heads * (dim + rot_dim)]")
+    if q.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)) or q.stride(1) != 1:
+        raise KernelError("latent_heads: q must be float32 [T, heads * (dim + rot_dim)] (may be a column slice)")
     if kfv.dtype != torch.float32 or tuple(kfv.shape) != (T, heads * (dim + value_dim)) or kfv.stride(1) != 1:
         raise KernelError("latent_heads: kfv must be float32 [T, heads * dim + heads * value_dim]")
     if hw < max(dim + rot_dim, value_dim) or rows.shape[0] != T or rows.shape[1] < kv_rank + rot_dim:
@@ -87,8 +93,8 @@ def latent_heads(q: torch.Tensor, kfv: torch.Tensor, rows: torch.Tensor, q_out: 
         if tuple(t.shape) != (T, heads * hw) or t.dtype != rows.dtype:
             raise KernelError("latent_heads: q_out, k_out, v_out must be [T, heads * hw] of rows' dtype")
     _check_tables(cos, sin, rot_dims, rot_dim)
-    need_contiguous(q=q, rows=rows, q_out=q_out, k_out=k_out, v_out=v_out, cos=cos, sin=sin)
-    check(core().tq_latent_heads(ptr(q), ptr(kfv), kfv.stride(0), heads * dim, ptr(rows), rows.shape[1], kv_rank, heads,
+    need_contiguous(rows=rows, q_out=q_out, k_out=k_out, v_out=v_out, cos=cos, sin=sin)
+    check(core().tq_latent_heads(ptr(q), q.stride(0), ptr(kfv), kfv.stride(0), heads * dim, ptr(rows), rows.shape[1], kv_rank, heads,
                                  dim, rot_dim, value_dim, hw, ptr(cos), ptr(sin), rot_dims, int(paired), ptr(tok_pos),
                                  ptr(q_out), ptr(k_out), ptr(v_out), dtype_code(q_out), T, stream()), "latent_heads")
 

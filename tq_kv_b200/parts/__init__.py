@@ -2,13 +2,14 @@
 from .attention import GQAttention
 from .base import (FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, StepBatch, StepContext, WeightSpec,
                    float32_vector)
-from .block import ParallelResidualBlock, PrenormResidualBlock
+from .block import ParallelResidualBlock, PostnormResidualBlock, PrenormResidualBlock
 from .decayed_state import DecayedStateMixer
 from .delta_rule import DeltaRuleMixer
 from .embedding import LMHead, TokenEmbedding
 from .feed_forward import SwiGLU
 from .gated_delta import GatedDeltaMixer
 from .latent_attention import LatentAttention
+from .mlstm import MatrixMemoryMixer
 from .norm import GroupRMSNorm, RMSNorm
 from .position import RotaryHalved, RotaryTables
 from .side_by_side import SideBySideMixer
@@ -33,6 +34,8 @@ register_part("gated_delta_mixer", GatedDeltaMixer, replace=True)
 register_part("gqa_attention", GQAttention, replace=True)
 register_part("softmax_attention", SoftmaxAttention, replace=True)
 register_part("table_experts", TableExperts, replace=True)
+register_part("routed_experts", TableExperts, replace=True)
+register_part("mlstm_mixer", MatrixMemoryMixer, replace=True)
 register_part("stream_connection", StreamConnection, replace=True)
 register_part("swiglu", SwiGLU, replace=True)
 register_part("token_embedding", TokenEmbedding, replace=True)
@@ -40,8 +43,9 @@ register_part("lm_head", LMHead, replace=True)
 register_block("prenorm_residual", PrenormResidualBlock, replace=True)
 register_block("parallel_residual", ParallelResidualBlock, replace=True)
 register_block("residual_streams", StreamsBlock, replace=True)
+register_block("postnorm_residual", PostnormResidualBlock, replace=True)
 
-__all__ = ["ResidualStreams", "SoftmaxAttention", "StreamConnection", "StreamsBlock", "TableExperts", "GatedDeltaMixer", "LatentAttention", "ParallelResidualBlock", "RotaryTables", "StateSpaceMixer", "DecayedStateMixer", "DeltaRuleMixer", "GroupRMSNorm", "SideBySideMixer", "SigmoidAttention",
+__all__ = ["MatrixMemoryMixer", "PostnormResidualBlock", "ResidualStreams", "SoftmaxAttention", "StreamConnection", "StreamsBlock", "TableExperts", "GatedDeltaMixer", "LatentAttention", "ParallelResidualBlock", "RotaryTables", "StateSpaceMixer", "DecayedStateMixer", "DeltaRuleMixer", "GroupRMSNorm", "SideBySideMixer", "SigmoidAttention",
            "FeedForward", "GQAttention", "LMHead", "Mixer", "Norm", "Part", "PositionEncoding",
            "PrenormResidualBlock", "RMSNorm", "RotaryHalved", "Runtime", "StepBatch", "StepContext", "SwiGLU",
            "TokenEmbedding", "WeightSpec", "float32_vector", "make_block", "make_part", "part_kinds",

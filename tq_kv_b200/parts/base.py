@@ -105,6 +105,11 @@ class StepContext:
     # True: the part's result REPLACES what `residual` holds (a buffer of its own that need not be cleared) instead
     # of being added to it.  A block sets it only for a part that says `can_store_result`.
     store_result: bool = False
+    # The schedule entry whose cache `kv` is (the running entry itself, or the earlier entry it reads), and a dict
+    # that lives for one step: an entry that brings a prompt's keys and values along as packed rows may leave them
+    # there for the entries that read its cache, which then need not find them in pages.
+    cache_entry: int = -1
+    step_shared: Optional[dict] = None
 
 
 class Part:

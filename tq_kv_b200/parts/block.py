@@ -82,3 +82,55 @@ class ParallelResidualBlock:
             self.feed_forward.forward(x, ctx, y)
         kernels.add_scaled(h, y, self.mult)
         kernels.mark("norms")
+
+
+class PostnormResidualBlock:
+    """h += norm1(mixer(h));  h += norm2(feed_forward(h)): the sublayers read the stream itself (rounded to the
+    activations' type where that is not float32) and the norm works on what they give.  Each sublayer stores its
+    result into a float32 buffer of its own (parts that say `can_store_result` write it without a cleared buffer);
+    one kernel then norms the buffer, adds it to the stream and leaves the rounded stream for the next reader.
+    The rounded stream travels from layer to layer as an attribute of the stream tensor, so a layer's first
+    sublayer does not round again what the layer before has rounded.  A layer may name no feed-forward."""
+    padded_rows_ok = True               # as far as its parts are
+
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.mixer = make_part(spec.part("mixer"))
+        self.mixer_norm = make_part(spec.part("mixer_norm"))
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_part(spec.part("feed_forward"))
+            self.feed_forward_norm = make_part(spec.part("feed_forward_norm"))
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm) if p is not None]
+
+    def forward(self, h, ctx: StepContext) -> None:
+        import torch
+        act = ctx.runtime.act_dtype
+        rounded = getattr(h, ROUNDED, None)
+        if rounded is not None:
+            delattr(h, ROUNDED)
+        for part, norm in ((self.mixer, self.mixer_norm), (self.feed_forward, self.feed_forward_norm)):
+            if part is None:
+                continue
+            if act == torch.float32:
+                x = h
+            else:
+                x = rounded if rounded is not None else kernels.round_rows(h)
+                kernels.mark("norms")
+            store = getattr(part, "can_store_result", False)
+            y = torch.empty_like(h) if store else torch.zeros_like(h)
+            ctx.store_result = store
+            try:
+                part.forward(x, ctx, y)
+            finally:
+                ctx.store_result = False
+            rounded = None if act == torch.float32 else torch.empty(h.shape, dtype=act, device=h.device)
+            kernels.add_normed_copy(h, y, norm.weight, norm.eps, rounded)
+            kernels.mark("norms")
+        if rounded is not None:
+            setattr(h, ROUNDED, rounded)
+
+
+ROUNDED = "_tq_rounded_copy"      # attribute of the stream tensor: the copy a block left for the next block's reader

@@ -1,6 +1,8 @@
-"""Dense SwiGLU feed-forward.  Reference: src/models/turbo_generic.rs:105-110
+"""Dense gated feed-forward.  Reference: src/models/turbo_generic.rs:105-110
 — down(silu(gate x) * (up x)), no biases; :1980 — residual sum.  Gate and up
-weights are concatenated at bind time so that one product yields both."""
+weights are concatenated at bind time so that one product yields both.
+`activation` names the gate's function: "silu" (the default, SwiGLU) or
+"gelu_tanh", 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))."""
 from __future__ import annotations
 
 import torch
@@ -12,9 +14,11 @@ from .base import FeedForward, Runtime, StepContext, WeightSpec
 class SwiGLU(FeedForward):
     takes_pending_norm = True           # x goes to kernels.linear only
     padded_rows_ok = True               # row by row
+    can_store_result = True
 
     def __init__(self, spec):
         super().__init__(spec)
+        self.activation = kernels.activation_code(self.params.get("activation", "silu"))
         self.hidden = int(self.params["hidden_size"])
         self.inter = int(self.params["intermediate_size"])
         self.names = dict(self.params.get("names", {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}))
@@ -37,7 +41,8 @@ class SwiGLU(FeedForward):
         self.w_down = tensors[self._n("down")].contiguous()
 
     def forward(self, x, ctx: StepContext, residual):
-        act = kernels.linear(x, self.w_gate_up, swiglu=True, out_dtype=ctx.runtime.act_dtype)
+        act = kernels.linear(x, self.w_gate_up, swiglu=True, activation=self.activation,
+                             out_dtype=ctx.runtime.act_dtype)
         kernels.mark("gate_up")
-        kernels.linear(act, self.w_down, out=residual, accumulate=True)
+        kernels.linear(act, self.w_down, out=residual, accumulate=not ctx.store_result)
         kernels.mark("down")

@@ -2,8 +2,21 @@
 
   values            "projected": v = W_v x;  "keys": there is no W_v, the values are
                     the keys as projected, before any rotation
-  position          a `rotary_tables` part (layout "halves"): q and k are rotated over
-                    their first rotary_dim entries; None: no rotation
+  position          a `rotary_tables` part: q and k are rotated over their first
+                    rotary_dim entries, entry i with i + rotary_dim/2 (layout "halves") or
+                    entry 2i with 2i + 1 (layout "pairs"); None: no rotation
+  row_norm_eps      q and k are RMS-normed over their WHOLE projections (all heads of a
+                    token at once, x / sqrt(mean(x^2) + eps) * weight, weights `q_norm` and
+                    `k_norm` of the projections' sizes) before the heads are split and rotated
+  sink              the softmax's denominator counts one more key of score 0 that has no
+                    value: p_j = exp(s_j) / (1 + sum exp(s))
+  shared_kv         the layer has no key/value tensors: it reads the cache of the schedule
+                    entry it is given (whose keys are stored normed and rotated) with its own
+                    queries, window and everything else
+  cache_window      the window the cache keeps (default: `window`; wider where other layers
+                    with wider windows read this layer's cache; None: all keys)
+  shares_packed     a prompt's packed keys and values are left in the step's shared dict for
+                    the layers that read this layer's cache
   qk_norm_eps       q and k are divided per head by their root mean square,
                     x / sqrt(mean(x^2) + eps), without a weight
   scale             s = q . k * scale
@@ -37,7 +50,7 @@ import torch
 from .. import kernels
 from ..cache import PAGE_TOKENS, KVRequest, ring_pages_for
 from ..config import ConfigError
-from .base import Mixer, Runtime, StepContext, WeightSpec
+from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
 from .registry import make_part
 
 
@@ -77,22 +90,37 @@ class SoftmaxAttention(Mixer):
             self.qk_norm_eps *= ratio
             self.scale *= ratio
         self.window: Optional[int] = int(p["window"]) if p.get("window") else None
+        self.cache_window: Optional[int] = self.window
+        if "cache_window" in p:
+            self.cache_window = int(p["cache_window"]) if p.get("cache_window") else None
+        if self.window is None and self.cache_window is not None:
+            raise ConfigError("softmax attention: a layer without a window needs a cache of all keys")
+        if self.window is not None and self.cache_window is not None and self.cache_window < self.window:
+            raise ConfigError(f"softmax attention: a cache of {self.cache_window} keys is too small for a window of {self.window}")
+        self.row_norm_eps = float(p["row_norm_eps"]) if p.get("row_norm_eps") else 0.0
+        self.sink = bool(p.get("sink", False))
+        self.shared_kv = bool(p.get("shared_kv", False))
+        self.shares_packed = bool(p.get("shares_packed", False))
+        if self.shared_kv and self.values != "projected":
+            raise ConfigError("softmax attention: a layer that reads another's cache has no keys to take its values from")
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
         self.output_gate = bool(p.get("output_gate", False))
         self.names = dict(p.get("names", {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o"}))
         kernels.check_row_widths(self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim)
         self.position = make_part(p["position"]) if p.get("position") is not None else None
         if self.position is not None:
-            if getattr(self.position, "layout", None) != "halves":
-                raise ConfigError("softmax attention rotates in the 'halves' layout (a rotary_tables part)")
+            if getattr(self.position, "layout", None) not in ("halves", "pairs"):
+                raise ConfigError("softmax attention rotates by a rotary_tables part (layout halves or pairs)")
             if self.position.rotary_dim > self.key_dim_given:
                 raise ConfigError(f"softmax attention: {self.position.rotary_dim} rotated entries in heads of "
                                   f"{self.key_dim_given}")
             if self.qk_norm_eps:
                 raise ConfigError("softmax attention: either a rotation or unit-size q and k, not both")
+        if self.qk_norm_eps and self.row_norm_eps:
+            raise ConfigError("softmax attention: q and k are normed per head or over the whole row, not both")
         self.q_width = self.n_heads * self.key_dim
-        self.k_width = self.n_kv_heads * self.key_dim
-        self.v_width = self.n_kv_heads * self.value_dim if self.values == "projected" else 0
+        self.k_width = 0 if self.shared_kv else self.n_kv_heads * self.key_dim
+        self.v_width = self.n_kv_heads * self.value_dim if self.values == "projected" and not self.shared_kv else 0
         self.o_width = self.n_heads * self.value_dim
         self.w_in = self.w_o = self.slopes = None
         self.window_chunk = 1
@@ -103,10 +131,15 @@ class SoftmaxAttention(Mixer):
 
     def weight_specs(self):
         d, e, H, G = self.key_dim_given, self.value_dim_given, self.n_heads, self.n_kv_heads
-        specs = [WeightSpec(self._n("q"), (H * d, self.hidden), "matrix"),
-                 WeightSpec(self._n("k"), (G * d, self.hidden), "matrix")]
-        if self.values == "projected":
-            specs.append(WeightSpec(self._n("v"), (G * e, self.hidden), "matrix"))
+        specs = [WeightSpec(self._n("q"), (H * d, self.hidden), "matrix")]
+        if not self.shared_kv:
+            specs.append(WeightSpec(self._n("k"), (G * d, self.hidden), "matrix"))
+            if self.values == "projected":
+                specs.append(WeightSpec(self._n("v"), (G * e, self.hidden), "matrix"))
+        if self.row_norm_eps:
+            specs.append(WeightSpec(self._n("q_norm"), (H * d,), "norm_scale"))
+            if not self.shared_kv:
+                specs.append(WeightSpec(self._n("k_norm"), (G * d,), "norm_scale"))
         if self.output_gate:
             specs.append(WeightSpec(self._n("gate"), (H * e, self.hidden), "matrix"))
         specs.append(WeightSpec(self._n("out"), (self.hidden, H * e), "matrix"))
@@ -122,7 +155,8 @@ class SoftmaxAttention(Mixer):
         return out.reshape(heads * padded, w.shape[1])
 
     def bind(self, tensors, runtime: Runtime, shared: Optional[dict] = None):
-        which = ["q", "k"] + (["v"] if self.values == "projected" else []) + (["gate"] if self.output_gate else [])
+        which = ["q"] + ([] if self.shared_kv else ["k"] + (["v"] if self.values == "projected" else [])) \
+            + (["gate"] if self.output_gate else [])
         heads = {"q": (self.n_heads, self.key_dim_given, self.key_dim),
                  "k": (self.n_kv_heads, self.key_dim_given, self.key_dim),
                  "v": (self.n_kv_heads, self.value_dim_given, self.value_dim),
@@ -135,8 +169,18 @@ class SoftmaxAttention(Mixer):
         if self.value_dim != self.value_dim_given:           # zero columns where the heads were padded
             w_o = self._pad_heads(w_o.t(), self.n_heads, self.value_dim_given, self.value_dim).t()
         self.w_o = w_o.contiguous()
-        self.k_col = self.q_width
-        self.v_col = self.k_col + self.k_width if self.values == "projected" else -1
+        self.k_col = 0 if self.shared_kv else self.q_width
+        self.v_col = self.q_width + self.k_width if self.values == "projected" and not self.shared_kv else -1
+        self.q_norm_w = self.k_norm_w = None
+        if self.row_norm_eps:                               # weights over the whole rows, padded like the heads
+            def padded(name, heads):
+                w = float32_vector(tensors[self._n(name)]).reshape(heads, self.key_dim_given)
+                out = w.new_zeros((heads, self.key_dim))
+                out[:, :self.key_dim_given] = w
+                return out.reshape(-1).contiguous()
+            self.q_norm_w = padded("q_norm", self.n_heads)
+            if not self.shared_kv:
+                self.k_norm_w = padded("k_norm", self.n_kv_heads)
         self.g_col = self.q_width + self.k_width + self.v_width
         if self.slope_exponent is not None:
             h = torch.arange(1, self.n_heads + 1, dtype=torch.float64)
@@ -150,24 +194,29 @@ class SoftmaxAttention(Mixer):
     # ---- cache ------------------------------------------------------------
     @property
     def _ring(self) -> bool:
-        return self.window is not None and self.keep_first == 0
+        return self.cache_window is not None and self.keep_first == 0
 
     def cache_request(self):
-        return KVRequest(self.n_kv_heads, self.key_dim, self.window if self._ring else None,
+        if self.shared_kv:
+            return None
+        return KVRequest(self.n_kv_heads, self.key_dim, self.cache_window if self._ring else None,
                          self.value_dim if self.value_dim != self.key_dim else None)
 
     def _use_packed(self, start_pos, step_lens, owns_cache) -> bool:
-        """Prompts that start at position 0 and own their cache attend over the step's own keys."""
-        return owns_cache and all(s == 0 for s in start_pos) and any(n > 1 for n in step_lens)
+        """Prompts that start at position 0 attend over the step's own keys: their own, or (a layer that reads
+        another's cache) the ones that layer left in the step's shared dict."""
+        return (owns_cache or self.shared_kv) and all(s == 0 for s in start_pos) and any(n > 1 for n in step_lens)
 
     def check_step(self, start_pos, step_lens, owns_cache):
+        if self.shared_kv and owns_cache:
+            raise kernels.KernelError("a layer without keys and values of its own must be given another entry's cache")
         if not self._ring or self._use_packed(start_pos, step_lens, owns_cache):
             return
-        ring_tokens = ring_pages_for(self.window, self.window_chunk - 1) * PAGE_TOKENS
+        ring_tokens = ring_pages_for(self.cache_window, self.window_chunk - 1) * PAGE_TOKENS
         longest = max(step_lens)
         if longest > ring_tokens - self.window + 1:
             raise kernels.KernelError(
-                f"a layer with a window of {self.window} keeps {ring_tokens} keys per sequence and cannot continue "
+                f"a layer with a window of {self.cache_window} keeps {ring_tokens} keys per sequence and cannot continue "
                 f"a sequence by {longest} tokens in one step (at most {ring_tokens - self.window + 1}; the engine's "
                 f"window_chunk option sets this)")
 
@@ -176,19 +225,33 @@ class SoftmaxAttention(Mixer):
         b, kv, dev = ctx.batch, ctx.kv, x.device
         T = x.shape[0]
         act = ctx.runtime.act_dtype
-        owns = kv is not None and kv.writes
+        owns = kv is not None and kv.writes and not self.shared_kv
         packed = self._use_packed(b.host_start, b.host_lens, owns)
         proj = kernels.linear(x, self.w_in, out_dtype=torch.float32)
         kernels.mark("qkv")
         q = torch.empty((T, self.q_width), dtype=act, device=dev)
-        k = torch.empty((T, self.k_width), dtype=act, device=dev) if packed else None
-        v = torch.empty((T, self.n_kv_heads * self.value_dim), dtype=act, device=dev) if packed else None
+        k = v = None
+        if packed and self.shared_kv:
+            k, v = ctx.step_shared[("packed_kv", ctx.cache_entry)]
+        elif packed:
+            k = torch.empty((T, self.k_width), dtype=act, device=dev)
+            v = torch.empty((T, self.n_kv_heads * self.value_dim), dtype=act, device=dev)
+            if self.shares_packed and ctx.step_shared is not None:
+                ctx.step_shared[("packed_kv", ctx.entry)] = (k, v)
         pos = self.position
+        row_inv = None
+        if self.row_norm_eps:
+            row_inv = kernels.row_inv_rms(proj, q_col=0, q_width=self.q_width, q_count=self.n_heads * self.key_dim_given,
+                                          k_col=self.k_col, k_width=self.k_width,
+                                          k_count=self.n_kv_heads * self.key_dim_given, eps=self.row_norm_eps)
         kernels.head_encode(
             proj, (b.tok_pos, b.tok_seq, b.new_lens), q, q_col=0, k_col=self.k_col, v_col=self.v_col,
-            n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
+            n_heads=self.n_heads, n_kv_heads=0 if self.shared_kv else self.n_kv_heads, key_dim=self.key_dim,
+            value_dim=self.value_dim, row_inv=row_inv, q_weight=self.q_norm_w, k_weight=self.k_norm_w,
+            paired=pos is not None and pos.paired,
             cos=pos.cos if pos is not None else None, sin=pos.sin if pos is not None else None,
-            rotary_dim=pos.rotary_dim if pos is not None else 0, norm_eps=self.qk_norm_eps, k_out=k, v_out=v,
+            rotary_dim=pos.rotary_dim if pos is not None else 0, norm_eps=self.qk_norm_eps,
+            k_out=None if self.shared_kv else k, v_out=None if self.shared_kv else v,
             k_pages=kv.k_pages if owns else None, v_pages=kv.v_pages if owns else None,
             block_table=kv.block_table if owns else None, table_width=kv.table_width if owns else 0,
             ring_pages=kv.ring_pages if owns else 0, page_tokens=kv.page_tokens if kv is not None else PAGE_TOKENS)
@@ -197,7 +260,7 @@ class SoftmaxAttention(Mixer):
         common = dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, key_dim=self.key_dim,
                       value_dim=self.value_dim, tok_pos=b.tok_pos, tok_seq=b.tok_seq, cu_seqlens=b.cu_seqlens,
                       start_pos=b.start_pos, scale=self.scale, window=self.window, keep_first=self.keep_first,
-                      softcap=self.softcap, slopes=self.slopes,
+                      softcap=self.softcap, slopes=self.slopes, sink=self.sink,
                       gate=proj[:, self.g_col:self.g_col + self.o_width] if self.output_gate else None)
         if packed:
             kernels.attention_ext(q, out, k_packed=k, v_packed=v, **common)
