@@ -26,11 +26,12 @@ then 256 decode steps.  Peaks come from MEASURED_PEAKS.json beside this file
 if it exists, else from an earlier measurement on the same kind of machine
 (6.65 TB/s, 1.59 PFLOP/s).
 
-`--design zodosun|rirudra|pavisun [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the named decoder beside the Qwen2
+`--design zodosun|rirudra|pavisun|furesun [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the named decoder beside the Qwen2
 decoder of the same width, depth, heads, feed-forward and vocabulary (random weights, bfloat16): device time of a
 prompt, of decode steps at batch 8 and 64, and the time by class of kernel with what the attention and scan
 kernels reach of their rooflines, as one JSON line of its own (`--design rirudra` also runs the Zodosun decoder,
-whose scans are the like kernels of its own; `--design pavisun` runs the Pavisun decoder and the Qwen2 decoder only).  The default workload and its line are untouched.
+whose scans are the like kernels of its own; `--design pavisun` runs the Pavisun decoder and the Qwen2 decoder only;
+`--design furesun` runs the Furesun, Rirudra and Qwen2 decoders).  The default workload and its line are untouched.
 
 The reference arm (`--impl reference`) cannot run here: the reference is a
 Rust workspace and no Rust toolchain is installed, so it prints its
@@ -252,6 +253,87 @@ def pavisun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
             "layers": [unit if i % 2 == 0 else rot for i in range(layers)]}
 
 
+FURESUN_WINDOW, FURESUN_EXPERTS, FURESUN_TOP = 1024, 8, 2
+
+
+def furesun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
+    """A Furesun configuration of the given width, heads of 128: attention through a latent of 96 values and a
+    rotated part of 32 (rotation stretched 8 times, a window of 1,024) with a dense gelu feed-forward; a matrix
+    memory with heads of 128 x 128; softmax attention on a quarter as many key heads (whole-row q/k norm, capped
+    scores, a window of 1,024, a sink); the same attention reading the third layer's keys; the last three layers
+    with 8 experts of a quarter of the feed-forward width of which a token uses 2, and a shared expert of half of it
+    (as many products per token as the dense feed-forward has); capped logits."""
+    heads, kv = width // 128, max(1, width // 512)
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2},
+           "router": {"experts": FURESUN_EXPERTS, "top": FURESUN_TOP, "scale": 2.0}}
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "heads": heads, "dim": 96, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "scale": 128 ** -0.5,
+        "mask": {"size": FURESUN_WINDOW},
+        "rot": {"base": 1e4, "dims": 32, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    memory = {"type": "mlstm", "mlp": moe, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}}
+    attn = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "mask": {"size": FURESUN_WINDOW}, "rot": {"base": 1e6, "dims": 64}}
+    order = [latent, memory, {"type": "attention", "mlp": moe, "mixer": attn},
+             {"type": "attention", "mlp": moe, "mixer": {**attn, "kv_from": 2}}]
+    return {"architecture": "Furesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "max_positions": 8192, "layers": [order[i] for i in range(min(layers, 4))]}
+
+
+def furesun_roofline(rec: dict, pk: dict, P: int, sms: int) -> dict:
+    """What the classes of the Furesun decoder reach of their rooflines, beside the like classes of the Qwen2
+    decoder (attention, feed-forward, the kernels between the sublayers) and of the Rirudra decoder (the scan)."""
+    width, ff, layers = rec["width"], rec["ff"], rec["layers"]
+    heads, kv, d = width // 128, max(1, width // 512), 128
+    f, q, r = rec["furesun"], rec["qwen2"], rec["rirudra"]
+    Wd, E, top = FURESUN_WINDOW, FURESUN_EXPERTS, FURESUN_TOP
+    fp32_tflops = 2 * FP32_FMA_PER_SM_PER_CLOCK * sms * 1900.0 * 1e6 / 1e12
+
+    def frac_tensor(flops, us):
+        return round(flops / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+
+    def frac_hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+
+    seen = sum(min(i + 1, Wd) for i in range(P))                        # keys a prompt's rows see in a window
+    roof = {"fp32_fma_tflops_nominal": round(fp32_tflops, 1)}
+    roof["furesun.prefill.attention.frac_of_bf16"] = frac_tensor(4 * heads * d * seen * 3, f["prefill_classes_us"]["attention"])
+    roof["qwen2.prefill.attention.frac_of_bf16"] = frac_tensor(
+        4 * heads * d * P * (P + 1) / 2 * layers, q["prefill_classes_us"]["attention"])
+    # the memory: per token and head 2 d e' multiply-adds for the update and 2 d e' for the read, e' = 132 columns
+    state = heads * 128 * 132
+    roof["furesun.prefill.scan.frac_of_fp32_fma"] = round(
+        P * 5 * state / (f["prefill_classes_us"]["scan"] * 1e-6) / 1e12 / fp32_tflops, 3)
+    ssm_state, delta_state = (2 * width // 64) * 128 * 64, heads * 128 * 128
+    roof["rirudra.prefill.scan.frac_of_fp32_fma"] = round(
+        P * (5 * ssm_state + 8 * delta_state) / (r["prefill_classes_us"]["scan"] * 1e-6) / 1e12 / fp32_tflops, 3)
+    roof["furesun.decode_b64.scan.frac_of_hbm"] = frac_hbm(64 * state * 4 * 2, f["decode_b64_classes_us"]["scan"])
+    roof["rirudra.decode_b64.scan.frac_of_hbm"] = frac_hbm(
+        64 * (ssm_state + delta_state) * 4 * 2, r["decode_b64_classes_us"]["scan"])
+    # the feed-forwards of a prompt: one dense layer and three of experts (2 of 8 small ones and the shared one)
+    ff_flops = 6 * P * width * ff
+    roof["furesun.prefill.feed_forward.frac_of_bf16"] = frac_tensor(
+        ff_flops * 4, sum(f["prefill_classes_us"].get(k, 0.0) for k in ("gate_up", "down", "experts", "shared_expert")))
+    roof["qwen2.prefill.feed_forward.frac_of_bf16"] = frac_tensor(
+        ff_flops * layers, q["prefill_classes_us"]["gate_up"] + q["prefill_classes_us"]["down"])
+    # between the sublayers: the sublayer's float32 result read, the stream read and written, a rounded copy written;
+    # the plain decoder reads the stream and writes a rounded norm (its sum rides in a product's last step)
+    roof["furesun.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(
+        P * width * (4 + 4 + 4 + 2) * 2 * 4, f["prefill_classes_us"]["norms"])
+    roof["qwen2.prefill.between_sublayers.frac_of_hbm"] = frac_hbm(
+        P * width * (4 + 2) * 2 * layers, q["prefill_classes_us"]["norms"])
+    keys = min(P + 16, Wd)
+    roof["furesun.decode_b64.attention.frac_of_hbm"] = frac_hbm(
+        64 * keys * (128 * 2 + 2 * 2 * kv * d * 2), f["decode_b64_classes_us"]["attention"])
+    roof["qwen2.decode_b64.attention.frac_of_hbm"] = frac_hbm(
+        64 * (P + 16) * 2 * kv * d * 2 * layers, q["decode_b64_classes_us"]["attention"])
+    roof["furesun.decode_b64.feed_forward.frac_of_hbm"] = frac_hbm(
+        3 * width * 2 * (ff + 3 * (E * (ff // 4) + ff // 2)),
+        sum(f["decode_b64_classes_us"].get(k, 0.0) for k in ("gate_up", "down", "experts", "shared_expert")))
+    roof["qwen2.decode_b64.feed_forward.frac_of_hbm"] = frac_hbm(
+        3 * width * ff * 2 * layers, q["decode_b64_classes_us"]["gate_up"] + q["decode_b64_classes_us"]["down"])
+    return roof
+
+
 def pavisun_roofline(rec: dict, pk: dict, P: int) -> dict:
     """What the classes of the Pavisun decoder reach of their rooflines, beside the like classes of the Qwen2
     decoder: attention (tensor throughput in a prompt, key and value bytes in decoding), the feed-forward (tensor
@@ -362,6 +444,9 @@ def design_compare(args) -> int:
                 models.insert(0, ("rirudra", rirudra_config(width, ff, layers, vocab)))
             if args.design == "pavisun":
                 models = [("pavisun", pavisun_config(width, ff, layers, vocab)), ("qwen2", qwen)]
+            if args.design == "furesun":
+                models = [("furesun", furesun_config(width, ff, layers, vocab)),
+                          ("rirudra", rirudra_config(width, ff, layers, vocab)), ("qwen2", qwen)]
             for model, cfg in models:
                 eng = tq.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=64, max_context=ctx,
                                             max_tokens=64 * ctx)
@@ -432,6 +517,9 @@ def design_compare(args) -> int:
             if args.design == "pavisun":
                 rec["roofline"] = pavisun_roofline(rec, pk, P)
                 continue
+            if args.design == "furesun":
+                rec["roofline"] = furesun_roofline(rec, pk, P, sms)
+                continue
             # what the classes reach of their rooflines
             heads, d = width // 128, 128
             z, q = rec["zodosun"], rec["qwen2"]
@@ -464,7 +552,7 @@ def design_compare(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zodosun", "rirudra", "pavisun"],
+    ap.add_argument("--design", default=None, choices=["zodosun", "rirudra", "pavisun", "furesun"],
                     help="instead of the default workload: this design beside the Qwen2 decoder of equal size")
     ap.add_argument("--sizes", default="1k,2k,4k", help="with --design: which of the sizes 1k, 2k, 4k (the model's width)")
     ap.add_argument("--gpus", type=int, default=1)

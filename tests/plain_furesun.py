@@ -19,6 +19,16 @@ import torch
 from plain_zodosun import read_folder, write_folder  # noqa: F401  (the file format is the same)
 
 
+# With a rounding function set (decoder(..., rounding=f)) the values that a 16-bit engine rounds are rounded here
+# too: what a sublayer reads, q, k and v as the attention takes them, and what goes into an output or down product.
+_rounding = [None]
+_margins = [None]        # a list while decoder(..., margins_out=list) runs: per routed layer, each token's router margin
+
+
+def _r(x):
+    return x if _rounding[0] is None else _rounding[0](x)
+
+
 # --------------------------------------------------------------------------
 # mechanisms
 # --------------------------------------------------------------------------
@@ -131,8 +141,8 @@ def latent_attention(x, w, p, c, positions, eps):
     val = (lat @ w[p + "uv"].T).reshape(T, H, e)
     qq = torch.cat([q[..., :d], q_r], dim=-1)
     kk = torch.cat([k_flat, k_r.expand(T, H, r)], dim=-1)
-    o = softmax_heads(qq, kk, val, c["scale"], visible(T, (c.get("mask") or {}).get("size")))
-    return o.reshape(T, H * e) @ w[p + "o"].T
+    o = softmax_heads(_r(qq), _r(kk), _r(val), c["scale"], visible(T, (c.get("mask") or {}).get("size")))
+    return _r(o.reshape(T, H * e)) @ w[p + "o"].T
 
 
 def mlstm(x, w, p, c, eps):
@@ -162,7 +172,7 @@ def mlstm(x, w, p, c, eps):
         den = torch.maximum((n * q[t]).sum(dim=-1).abs(), torch.exp(-m)) + 1e-6
         out[t] = num / den.reshape(H, 1)
     y = rms(out, eps).reshape(T, H * e) * w[p + "norm"] * torch.sigmoid(x @ w[p + "g"].T)
-    return y @ w[p + "o"].T
+    return _r(y) @ w[p + "o"].T
 
 
 def attention_keys(x, w, p, c, positions, eps):
@@ -173,7 +183,7 @@ def attention_keys(x, w, p, c, positions, eps):
     k = rms_norm(x @ w[p + "k"].T, w[p + "k.norm"], eps).reshape(T, G, d)
     k = rotate(k, positions, rot["dims"], rot["base"], "pairs", rot.get("scaling"))
     v = (x @ w[p + "v"].T).reshape(T, G, e)
-    return k, v
+    return _r(k), _r(v)
 
 
 def attention(x, w, p, c, positions, eps, kv=None):
@@ -186,20 +196,27 @@ def attention(x, w, p, c, positions, eps, kv=None):
     q = rms_norm(x @ w[p + "q"].T, w[p + "q.norm"], eps).reshape(T, H, d)
     q = rotate(q, positions, rot["dims"], rot["base"], "pairs", rot.get("scaling"))
     k, v = kv if kv is not None else attention_keys(x, w, p, c, positions, eps)
-    o = softmax_heads(q, k, v, c["scale"], visible(T, (c.get("mask") or {}).get("size")), cap=c.get("softcap"), sink=True)
-    return o.reshape(T, H * e) @ w[p + "o"].T
+    o = softmax_heads(_r(q), k, v, c["scale"], visible(T, (c.get("mask") or {}).get("size")), cap=c.get("softcap"), sink=True)
+    return _r(o.reshape(T, H * e)) @ w[p + "o"].T
 
 
 def gated_ff(x, w, p, act):
-    return (act(x @ w[p + "gate"].T) * (x @ w[p + "up"].T)) @ w[p + "down"].T
+    return _r(act(x @ w[p + "gate"].T) * (x @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def routed_ff(x, w, p, c):
     """Scores sigma(W_router x); the `top` largest are chosen; their scores over their sum (+ 1e-20) times
     router.scale weigh the chosen experts' results; a shared expert is added for every token."""
     r = c["router"]
-    s = torch.sigmoid(x @ w[p + "router"].T)
-    val, idx = torch.topk(s, r["top"], dim=-1)
+    z = x @ w[p + "router"].T
+    s = torch.sigmoid(z)
+    val, idx = torch.topk(z, r["top"], dim=-1)              # (the logits' order is the scores' order)
+    val = torch.sigmoid(val)
+    if _margins[0] is not None:
+        # how far the last chosen logit lies above the first one left out, relative to the logits' root mean square
+        zs = torch.sort(z, dim=-1, descending=True).values
+        gap = zs[:, r["top"] - 1] - zs[:, r["top"]] if r["top"] < z.shape[1] else torch.full_like(zs[:, 0], math.inf)
+        _margins[0].append(gap / (torch.sqrt((z * z).mean(dim=-1)) + 1e-9))
     wts = val / (val.sum(dim=-1, keepdim=True) + 1e-20) * r["scale"]
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
@@ -219,8 +236,20 @@ def feed_forward(x, w, p, c):
 # --------------------------------------------------------------------------
 # the decoder
 # --------------------------------------------------------------------------
-def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, layers_out=None) -> torch.Tensor:
-    """Logits [T, vocab] of a whole sequence.  `layers_out` (a list) receives the stream after every layer."""
+def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, layers_out=None, rounding=None,
+            margins_out=None):
+    """Logits [T, vocab] of a whole sequence.  `layers_out` (a list) receives the stream after every layer.
+    `rounding`: a function applied where a 16-bit engine rounds its activations.  `margins_out` (a list) receives,
+    per routed feed-forward, each token's router margin: the gap between the last chosen logit and the first one
+    left out over the root mean square of the token's logits; a small margin is a choice that rounding can turn."""
+    _rounding[0], _margins[0] = rounding, margins_out
+    try:
+        return _decoder(cfg, weights, tokens, dtype, layers_out)
+    finally:
+        _rounding[0] = _margins[0] = None
+
+
+def _decoder(cfg, weights, tokens, dtype, layers_out):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
     T = len(tokens)
@@ -229,24 +258,25 @@ def decoder(cfg: dict, weights: dict, tokens: list[int], dtype=torch.float64, la
     kept: dict[int, tuple] = {}
     for i, layer in enumerate(cfg["layers"]):
         p, c = f"l{i}.mix.", layer["mixer"]
+        xr = _r(x)                                            # what the sublayer reads
         if layer["type"] == "latent_attention":
-            y = latent_attention(x, w, p, c, positions, eps)
+            y = latent_attention(xr, w, p, c, positions, eps)
         elif layer["type"] == "mlstm":
-            y = mlstm(x, w, p, c, eps)
+            y = mlstm(xr, w, p, c, eps)
         elif layer["type"] == "attention":
             if c.get("kv_from") is not None:
-                y = attention(x, w, p, c, positions, eps, kv=kept[int(c["kv_from"])])
+                y = attention(xr, w, p, c, positions, eps, kv=kept[int(c["kv_from"])])
             else:
-                kept[i] = attention_keys(x, w, p, c, positions, eps)
-                y = attention(x, w, p, c, positions, eps, kv=kept[i])
+                kept[i] = attention_keys(xr, w, p, c, positions, eps)
+                y = attention(xr, w, p, c, positions, eps, kv=kept[i])
         else:
             raise ValueError(f"unknown layer type {layer['type']}")
         x = x + rms_norm(y, w[f"l{i}.norm1"], eps)
         if layer.get("mlp") is not None:
-            x = x + rms_norm(feed_forward(x, w, f"l{i}.mlp.", layer["mlp"]), w[f"l{i}.norm2"], eps)
+            x = x + rms_norm(feed_forward(_r(x), w, f"l{i}.mlp.", layer["mlp"]), w[f"l{i}.norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = _r(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     if cfg.get("logit_softcap"):
         logits = tanh_cap(logits, float(cfg["logit_softcap"]))
     return logits

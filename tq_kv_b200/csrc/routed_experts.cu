@@ -39,7 +39,9 @@ TQ_API int tq_table_choice(const int* tokens, const int* table, int vocab, int t
 
 // ---- choice: experts of each token from a router's logits -------------------------------------------------------
 // scores s = sigmoid(logit); the `top` largest are chosen (the lowest index first among equals); their weights
-// are  scale * s / (sum of the chosen s + floor).  A warp per token; float32 throughout.
+// are  scale * s / (sum of the chosen s + floor).  The choice compares the logits themselves: the sigmoid keeps
+// their order, but in float32 it is 1 for every logit above 17 and would make equals of them.  A warp per token;
+// float32 throughout.
 __global__ void __launch_bounds__(128)
 router_choice_kernel(const float* __restrict__ logits, int ld, int n_experts, int top, float scale, float floor_,
                      int* __restrict__ choice, float* __restrict__ weights, int n_tokens) {
@@ -50,23 +52,24 @@ router_choice_kernel(const float* __restrict__ logits, int ld, int n_experts, in
     const float* z = logits + (size_t)t * ld;
     float total = 0.f;
     for (int s = 0; s < top; ++s) {
-        float best = -1.f;
-        int best_e = n_experts;
+        float best = 0.f;
+        int best_e = n_experts;                           // n_experts: this lane has found none yet
         for (int e = lane; e < n_experts; e += 32) {
             bool taken = false;
             for (int r = 0; r < s; ++r) taken |= choice[t * top + r] == e;
-            const float v = 1.f / (1.f + expf(-z[e]));
-            if (!taken && v > best) { best = v; best_e = e; }
+            const float v = z[e];                        // the order of the logits is the order of the scores
+            if (!taken && (best_e == n_experts || v > best)) { best = v; best_e = e; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            if (oe < n_experts && (best_e == n_experts || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
         }
-        if (lane == 0) { choice[t * top + s] = best_e; weights[t * top + s] = best; }
+        const float score = 1.f / (1.f + expf(-best));
+        if (lane == 0) { choice[t * top + s] = best_e; weights[t * top + s] = score; }
         __syncwarp();
-        total += best;
+        total += score;
     }
     const float f = scale / (total + floor_);
     for (int s = lane; s < top; s += 32) weights[t * top + s] *= f;
