@@ -84,6 +84,9 @@ __device__ __forceinline__ void dg_ld32(uint32_t taddr, float* v) {
 // summed on the way, each block over its share of K, and the shares meet with the partial products in the
 // cluster's exchange, where every output is scaled by 1 / sqrt(mean(h^2) + eps) of its batch row.  So the norm
 // needs no kernel and no trip through memory of its own.
+// The gate's activation of a gated product (TQ_ACT_*): the exported functions set it from their `swiglu` argument
+// (1 or 2; 0: not gated) right before they launch, on the launching thread.
+static thread_local int dg_gate_act = TQ_ACT_SILU;
 #define DG_NORM_ROWS 16
 #define DG_HRING 4
 template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool REDUCE, bool NORM = false>
@@ -92,7 +95,7 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                       const __grid_constant__ CUtensorMap map_y, const float* __restrict__ bias, TO* __restrict__ Y,
                       int M, int N, int K, int ldy, int accumulate, int k_splits, int* __restrict__ status,
                       const float* __restrict__ H = nullptr, int ldh = 0, const float* __restrict__ G = nullptr,
-                      float eps = 0.f) {
+                      float eps = 0.f, int act = TQ_ACT_SILU) {
     static_assert(!NORM || (!REDUCE && MP == 32), "the folded norm runs in the cluster form with up to 16 rows");
     constexpr int X_BYTES = MP * DG_BK * 2;
     constexpr int STAGE_BYTES = DG_W_BYTES + X_BYTES;
@@ -404,7 +407,7 @@ decode_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
                 if (bias) { v += bias[col]; if (SWIGLU) w += bias[col + N]; }
                 if (SWIGLU)            // (a bfloat16 result keeps 8 bits: the fast exponential and division do)
-                    v = sizeof(TO) == 2 ? __fdividef(v, 1.f + __expf(-v)) * w : (v / (1.f + expf(-v))) * w;
+                    v = (sizeof(TO) == 2 ? gated_act_fast(v, act) : gated_act(v, act)) * w;
                 TO* y = Y + (size_t)m * ldy + col;
                 if (accumulate) v += to_f32<TO>(*y);
                 *y = from_f32<TO>(v);
@@ -464,7 +467,7 @@ static int dg_launch_reduce(const CUtensorMap& mw, const CUtensorMap& mx, const 
     const int tiles = (N + DG_ROWS - 1) / DG_ROWS;
     return tq_launch_pdl(TQ_PDL_DECODE_GEMM, decode_gemm_tc_kernel<MP, false, float, STAGES, true>, dim3(tiles * splits), dim3(DG_THREADS),
                          SMEM, stream, mw, mx, my, bias, Y, M, N, K, ldy, accumulate, splits, status, (const float*)nullptr, 0,
-                         (const float*)nullptr, 0.f);
+                         (const float*)nullptr, 0.f, TQ_ACT_SILU);
 }
 
 template <int MP, bool SWIGLU, typename TO, int DG_STAGES, bool NORM = false>
@@ -499,7 +502,7 @@ static int dg_launch_s(const CUtensorMap& mw, const CUtensorMap& mx, const float
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gemm_tc_kernel<MP, SWIGLU, TO, DG_STAGES, false, NORM>, mw, mx,
                                        mw /* no map of Y in this form */, bias, (TO*)Y, M, N, K, ldy, accumulate, 1,
-                                       status, H, ldh, G, eps);
+                                       status, H, ldh, G, eps, dg_gate_act);
     if (e != cudaSuccess) return (int)e;
     return tq_launch_status();
 }
@@ -554,6 +557,8 @@ TQ_API int tq_decode_gemm_tc(const void* X, const void* W, const float* bias, vo
     if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
         return (int)cudaErrorInvalidValue;
     if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    if (swiglu != 0 && swiglu != TQ_ACT_SILU && swiglu != TQ_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+    dg_gate_act = swiglu ? swiglu : TQ_ACT_SILU;
     const int mp = M <= 32 ? 32 : 64;
     CUtensorMap mw, mx;
     int st = dg_make_map(&mw, W, swiglu ? 2ull * N : (uint64_t)N, (uint64_t)K, (uint64_t)ldw,
@@ -589,6 +594,8 @@ TQ_API int tq_decode_gemm_tc_norm(const float* H, const float* G, float eps, con
         (reinterpret_cast<uintptr_t>(G) & 15))
         return (int)cudaErrorInvalidValue;
     if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    if (swiglu != 0 && swiglu != TQ_ACT_SILU && swiglu != TQ_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+    dg_gate_act = swiglu ? swiglu : TQ_ACT_SILU;
     CUtensorMap mw;
     int st = dg_make_map(&mw, W, swiglu ? 2ull * N : (uint64_t)N, (uint64_t)K, (uint64_t)ldw,
                          swiglu ? DG_ROWS / 2 : DG_ROWS);

@@ -51,6 +51,8 @@
 #define EPI_STORE 0
 #define EPI_ACCUM 1
 #define EPI_SWIGLU 2
+#define EPI_GELU 3          // as EPI_SWIGLU with the tanh form of gelu on the gate
+#define TC_GATED(E) ((E) == EPI_SWIGLU || (E) == EPI_GELU)
 
 // ---- PTX wrappers -------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -141,23 +143,24 @@ template <int EPI, typename TO>
 __device__ __forceinline__ void tc_epilogue_item(uint32_t t_row, unsigned char* st, uint32_t& piece,
                                                  const CUtensorMap* map_c_ptr, const float* __restrict__ bias, int n0,
                                                  int row0, int M, int N, int part, int lane) {
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const bool rows_live = row0 < M;                  // a warp whose rows all lie past M stores nothing
 #pragma unroll 1
     for (int c = 0; c < OUT_COLS; c += 32) {
         if (n0 + c >= N) break;
         float v[32];
-        if (EPI == EPI_SWIGLU) {
+        if (TC_GATED(EPI)) {
             float u[32];
             tc_ld32(t_row + c, v);
             tc_ld32(t_row + TC_BN / 2 + c, u);
             tc_wait_ld();
-            // silu(g) * u.  A bfloat16 result keeps 8 bits: the fast exponential and division (2 ulp of float32)
+            // act(g) * u, act being silu or (EPI_GELU) the tanh form of gelu.  A bfloat16 result keeps 8 bits: the fast exponential and division (2 ulp of float32)
             // cost a third of the exact ones' instructions, which a short K cannot hide under its MMAs.
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                v[j] = sizeof(TO) == 2 ? __fdividef(v[j], 1.f + __expf(-v[j])) * u[j]
-                                       : (v[j] / (1.f + expf(-v[j]))) * u[j];
+            for (int j = 0; j < 32; ++j) {
+                constexpr int ACT = EPI == EPI_GELU ? TQ_ACT_GELU_TANH : TQ_ACT_SILU;
+                v[j] = (sizeof(TO) == 2 ? gated_act_fast(v[j], ACT) : gated_act(v[j], ACT)) * u[j];
+            }
         } else {
             tc_ld32(t_row + c, v);
             tc_wait_ld();
@@ -234,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // output columns of a tile; with SwiGLU a tile yields 128 outputs from 128 gate + 128 up rows of B
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const int tiles_m = (M + TC_BM - 1) / TC_BM;
     const int tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
     const int n_tiles = tiles_m * tiles_n;
@@ -299,7 +302,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     mbar_expect_tx(fb, TC_STAGE_BYTES);
                     const int kc = (k_lo + i) * TC_BK;
                     tma_load_2d(a_dst, &map_a, kc, m0, fb);
-                    if (EPI == EPI_SWIGLU) {
+                    if (TC_GATED(EPI)) {
                         tma_load_2d(b_dst, &map_b, kc, b_base + n0, fb);                                  // gate rows
                         tma_load_2d(b_dst + TC_B_BYTES / 2, &map_b, kc, b_base + b_rows_second + n0, fb); // up rows
                     } else {
@@ -447,7 +450,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                  // 0: issues the MMAs
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const int tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
     const int tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
     const int n_tiles = tiles_m * tiles_n;
@@ -499,7 +502,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 item(w, t, k_lo, k_iters, part);
                 const int m0 = (t % tiles_m) * 2 * TC_BM + (int)rank * TC_BM;
                 const int n0 = (t / tiles_m) * OUT_COLS;
-                const int b_row = EPI == EPI_SWIGLU ? (rank == 0 ? n0 : b_rows_second + n0) : n0 + (int)rank * (TC_BN / 2);
+                const int b_row = TC_GATED(EPI) ? (rank == 0 ? n0 : b_rows_second + n0) : n0 + (int)rank * (TC_BN / 2);
                 for (int i = 0; i < k_iters; ++i, ++it) {
                     const int s = it % T2_STAGES;
                     if (!mbar_wait(smem_u32(&empty[s]), ((it / T2_STAGES) & 1) ^ 1)) { *failed = 1; ok = false; break; }
@@ -630,7 +633,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
     const int sm_count = tc_sm_count();
     // The tiles of an incomplete last round (all tiles, if they are fewer than the SMs) are cut along K into
@@ -656,7 +659,7 @@ static int launch_tc_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
     const int sm_count = tc_sm_count();
     const int grid = n_tiles < sm_count ? n_tiles : sm_count;
@@ -675,7 +678,7 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CU
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? TC_BN / 2 : TC_BN;
+    constexpr int OUT_COLS = TC_GATED(EPI) ? TC_BN / 2 : TC_BN;
     const int n_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + 2 * TC_BM - 1) / (2 * TC_BM));
     const int pairs = tc_sm_count() / 2 > 0 ? tc_sm_count() / 2 : 1;
     int n_whole = n_tiles, parts = 1;
@@ -716,14 +719,15 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     // C leaves through TMA: 16-byte aligned base and row stride
     if ((reinterpret_cast<uintptr_t>(C) & 15) || ((size_t)ldc * (c_dtype == TQ_F32 ? 4 : 2)) % 16)
         return (int)cudaErrorInvalidValue;
-    if (epilogue == EPI_SWIGLU && (N & 1)) return (int)cudaErrorInvalidValue;
+    const bool gated = epilogue == EPI_SWIGLU || epilogue == EPI_GELU;
+    if (gated && (N & 1)) return (int)cudaErrorInvalidValue;
     CUtensorMap ma, mb;
     int st = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM);
     if (st) return st;
     const bool pair = tc_mode() == 2 || (tc_mode() == 0 && M > TC_BM);
-    const uint64_t b_rows = epilogue == EPI_SWIGLU ? 2ull * N : (uint64_t)N;
+    const uint64_t b_rows = gated ? 2ull * N : (uint64_t)N;
     // a block loads 128 rows of B at a time in the pair form and with SwiGLU, else the tile's 256
-    st = make_map(&mb, B, b_rows, (uint64_t)K, (uint64_t)ldb, (pair || epilogue == EPI_SWIGLU) ? TC_BN / 2 : TC_BN);
+    st = make_map(&mb, B, b_rows, (uint64_t)K, (uint64_t)ldb, (pair || gated) ? TC_BN / 2 : TC_BN);
     if (st) return st;
     CUtensorMap mc;
     st = make_map_c(&mc, C, c_dtype == TQ_F32, (uint64_t)M, (uint64_t)N, (uint64_t)ldc);
@@ -749,6 +753,8 @@ TQ_API int tq_gemm_tc(const void* A, const void* B, const float* bias, void* C, 
     if (epilogue == EPI_ACCUM) TQ_TC(EPI_ACCUM, float);
     if (epilogue == EPI_SWIGLU && c_dtype == TQ_F32) TQ_TC(EPI_SWIGLU, float);
     if (epilogue == EPI_SWIGLU && c_dtype == TQ_BF16) TQ_TC(EPI_SWIGLU, bf16);
+    if (epilogue == EPI_GELU && c_dtype == TQ_F32) TQ_TC(EPI_GELU, float);
+    if (epilogue == EPI_GELU && c_dtype == TQ_BF16) TQ_TC(EPI_GELU, bf16);
 #undef TQ_TC
     return (int)cudaErrorInvalidValue;
 }

@@ -47,11 +47,15 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // x = bfloat16(h * g) and scales each batch row's sums by 1 / sqrt(mean(h^2) + eps) before the epilogue, so
 // that the norm needs no kernel and no trip through memory of its own.  The sums of squares are gathered
 // beside the partial products (every k is read by exactly one lane of one warp of one block of the cluster).
+// The gate's activation of a gated product (TQ_ACT_*): the exported functions set it from their `swiglu` argument
+// (1 or 2; 0: not gated) right before they launch, on the launching thread.
+static thread_local int sk_gate_act = TQ_ACT_SILU;
+
 template <int NT, int TW, bool SWIGLU, typename TO, bool NORM>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 skinny_gemm_kernel(const void* __restrict__ Xv, const bf16* __restrict__ W, const float* __restrict__ bias,
                    TO* __restrict__ Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate,
-                   const float* __restrict__ G, float eps) {
+                   const float* __restrict__ G, float eps, int act) {
     constexpr int COLS = SWIGLU ? 16 : 16 * TW;          // output columns of this block
     constexpr int PER_WARP = TW * 16 * (8 * NT + 1);
     extern __shared__ float red_raw[];
@@ -228,7 +232,7 @@ skinny_gemm_kernel(const void* __restrict__ Xv, const bf16* __restrict__ W, cons
             }
             if (bias) { v += bias[col]; if (SWIGLU) u += bias[col + N]; }
             if (SWIGLU)                // (a bfloat16 result keeps 8 bits: the fast exponential and division do)
-                v = sizeof(TO) == 2 ? __fdividef(v, 1.f + __expf(-v)) * u : (v / (1.f + expf(-v))) * u;
+                v = (sizeof(TO) == 2 ? gated_act_fast(v, act) : gated_act(v, act)) * u;
             TO* y = Y + (size_t)m * ldy + col;
             if (accumulate) v += to_f32<TO>(*y);
             *y = from_f32<TO>(v);
@@ -269,7 +273,7 @@ static int launch_skinny(const void* X, const bf16* W, const float* bias, void* 
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TW, SWIGLU, TO, NORM>, X, W, bias, (TO*)Y, M, N, K,
-                                       ldx, ldw, ldy, accumulate, G, eps);
+                                       ldx, ldw, ldy, accumulate, G, eps, sk_gate_act);
     if (e != cudaSuccess) return (int)e;
     return tq_launch_status();
 }
@@ -298,6 +302,8 @@ TQ_API int tq_skinny_gemm(const void* X, const void* W, const float* bias, void*
     if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
         return (int)cudaErrorInvalidValue;
     if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    if (swiglu != 0 && swiglu != TQ_ACT_SILU && swiglu != TQ_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+    sk_gate_act = swiglu ? swiglu : TQ_ACT_SILU;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
     if (swiglu) {
@@ -321,6 +327,8 @@ TQ_API int tq_skinny_gemm_norm(const float* H, const float* G, float eps, const 
         (reinterpret_cast<uintptr_t>(G) & 15))
         return (int)cudaErrorInvalidValue;
     if (accumulate && y_dtype != TQ_F32) return (int)cudaErrorInvalidValue;
+    if (swiglu != 0 && swiglu != TQ_ACT_SILU && swiglu != TQ_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+    sk_gate_act = swiglu ? swiglu : TQ_ACT_SILU;
     const bf16* w = (const bf16*)W;
 #define TQ_SKN(NT, TW, S, T) \
     return launch_skinny<NT, TW, S, T, true>(H, w, bias, Y, M, N, K, ldh, ldw, ldy, accumulate, stream, G, eps)

@@ -94,19 +94,25 @@ def _tc_takes(rows: int, w: torch.Tensor, swiglu: bool, after_norm: bool, float3
     return size >= TC_DECODE_MIN_ADDED_BYTES or rows > TC_DECODE_ADDED_ROWS
 
 
-def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False):
+def _gate(swiglu, activation) -> int:
+    """The `swiglu` argument of the C functions: 0 for a plain product, else the gate's activation code."""
+    return int(activation) if swiglu else 0
+
+
+def skinny_gemm(x, w, out, bias=None, accumulate=False, swiglu=False, activation=elementwise.ACT_SILU):
     """bfloat16 x [M <= 64, K] times bfloat16 w [N, K]^T on the tensor cores,
     streaming w once (csrc/skinny_gemm.cu).  K must be a multiple of 32."""
     M, K = x.shape
     N = out.shape[1]
     check(core().tq_skinny_gemm(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
-                                w.stride(0), out.stride(0), int(accumulate), int(swiglu), stream()), "skinny_gemm")
+                                w.stride(0), out.stride(0), int(accumulate), _gate(swiglu, activation), stream()),
+          "skinny_gemm")
     return out
 
 
 # ---- tcgen05 + TMA product for many rows (csrc/gemm_tc.cu) -----------------------
 USE_TCGEN05 = True                  # False: the library product (cuBLAS) takes the many-row bfloat16 case
-EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_GELU = 0, 1, 2, 3
 
 
 def set_gemm_tc_mode(mode: int) -> None:
@@ -119,7 +125,7 @@ def set_gemm_tc_mode(mode: int) -> None:
 
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
     """out (=, +=) x · w^T on the tcgen05 tensor cores; with EPI_SWIGLU w holds
-    gate rows then up rows and out = silu(gate) * up.  bfloat16 operands, K a
+    gate rows then up rows and out = silu(gate) * up (EPI_GELU: the tanh form of gelu on the gate).  bfloat16 operands, K a
     multiple of 8, 16-byte aligned rows."""
     M, K = x.shape
     N = out.shape[1]
@@ -128,19 +134,19 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE):
     return out
 
 
-def decode_gemm_tc(x, w, out, bias=None, accumulate=False, swiglu=False):
+def decode_gemm_tc(x, w, out, bias=None, accumulate=False, swiglu=False, activation=elementwise.ACT_SILU):
     """bfloat16 x [M <= 64, K] times w [N, K]^T on the tcgen05 tensor cores
     with the operands swapped (csrc/decode_gemm_tc.cu): the weight streams once
     through TMA, K is split over a thread-block cluster where tiles are few."""
     M, K = x.shape
     N = out.shape[1]
     check(core().tq_decode_gemm_tc(ptr(x), ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, x.stride(0),
-                                   w.stride(0), out.stride(0), int(accumulate), int(swiglu),
+                                   w.stride(0), out.stride(0), int(accumulate), _gate(swiglu, activation),
                                    ptr(tc_status_word(x.device)), stream()), "decode_gemm_tc")
     return out
 
 
-def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
+def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu, activation=elementwise.ACT_SILU) -> bool:
     """Runs out (=, +=) norm(h) . w^T with the norm folded into a decode product; False if none takes it."""
     h, g = x.h, x.weight
     M, K = h.shape
@@ -160,7 +166,7 @@ def _fused_norm(x: "PendingNorm", w, out, bias, accumulate, swiglu) -> bool:
         return False
     N = out.shape[1]
     args = (ptr(h), ptr(g), x.eps, ptr(w), ptr(bias), ptr(out), dtype_code(out), M, N, K, h.stride(0), w.stride(0),
-            out.stride(0), int(accumulate), int(swiglu))
+            out.stride(0), int(accumulate), _gate(swiglu, activation))
     if big:
         check(core().tq_decode_gemm_tc_norm(*args, ptr(tc_status_word(h.device)), stream()), "decode_gemm_tc_norm")
     else:
@@ -244,34 +250,30 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = N
         raise KernelError("linear: bias must be float32 with one entry per weight row")
     if M == 0:
         return out
-    other_act = swiglu and activation != elementwise.ACT_SILU
     if pending is not None:
-        if not other_act and _fused_norm(pending, w, out, bias, accumulate, swiglu):
+        if _fused_norm(pending, w, out, bias, accumulate, swiglu, activation):
             return out
         x = pending.materialize()
-    if other_act and not (M <= ROW_KERNEL_MAX_ROWS and (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16)):
-        # the tensor-core kernels gate with silu: another activation runs after a plain product
-        y = linear(x, w, bias=bias, out_dtype=torch.float32)
-        return elementwise.swiglu(y, out, activation)
 
     # decoding: the TMA-fed tcgen05 kernel or the mma.sync kernel (_tc_takes says which, where both can)
     if (USE_TCGEN05 and M <= SKINNY_MAX_ROWS and _tc_ok(x, w, out, swiglu)
             and (not accumulate or out.dtype == torch.float32)
             and (not _skinny_ok(x, w)
                  or _tc_takes(M, w, bool(swiglu), pending is not None, out.dtype == torch.float32))):
-        return decode_gemm_tc(x, w, out, bias, accumulate, swiglu)
+        return decode_gemm_tc(x, w, out, bias, accumulate, swiglu, activation)
     if _skinny_ok(x, w):
-        return skinny_gemm(x, w, out, bias, accumulate, swiglu)
+        return skinny_gemm(x, w, out, bias, accumulate, swiglu, activation)
     if M <= ROW_KERNEL_MAX_ROWS:
         return gemv_rows(x, w, out, bias, accumulate, swiglu, activation)
 
     if _tc_ok(x, w, out, swiglu) and (not accumulate or out.dtype == torch.float32):
-        return gemm_tc(x, w, out, bias, EPI_SWIGLU if swiglu else (EPI_ACCUM if accumulate else EPI_STORE))
+        gated = EPI_GELU if activation == elementwise.ACT_GELU_TANH else EPI_SWIGLU
+        return gemm_tc(x, w, out, bias, gated if swiglu else (EPI_ACCUM if accumulate else EPI_STORE))
 
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)          # library product, float32 out
         if swiglu:
-            return elementwise.swiglu(y, out)
+            return elementwise.swiglu(y, out, activation)
         if accumulate:
             return elementwise.add_into(out, y)
         if out.dtype == torch.float32:
