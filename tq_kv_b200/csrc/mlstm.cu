@@ -39,17 +39,29 @@ mlstm_gates_kernel(const float* __restrict__ in_raw, const float* __restrict__ f
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     float* mp = state_m + (size_t)slots[b] * state_stride + h;
     float m = *mp;
+    // the raw gates of the chunk after this one are asked for before the chain of this one runs
+    float in_next = 0.f, f_next = 0.f;
+    if (t0 + lane < t1) {
+        in_next = in_raw[(size_t)(t0 + lane) * ld + h];
+        f_next = f_raw[(size_t)(t0 + lane) * ld + h];
+    }
     for (int base = t0; base < t1; base += 32) {
         const int t = base + lane;
         const bool valid = t < t1;
-        float ig = 0.f, fg = 0.f;
-        if (valid) {
-            ig = cap * tanhf(in_raw[(size_t)t * ld + h] / cap);
-            fg = log_sigmoid(cap * tanhf(f_raw[(size_t)t * ld + h] / cap));
+        const float in_now = in_next, f_now = f_next;
+        if (t + 32 < t1) {
+            in_next = in_raw[(size_t)(t + 32) * ld + h];
+            f_next = f_raw[(size_t)(t + 32) * ld + h];
         }
-        const int n_here = min(32, t1 - base);
+        // a lane past the sequence's end carries the gates that leave m as it is: f = 0, i = -inf
+        float ig = -INFINITY, fg = 0.f;
+        if (valid) {
+            ig = cap * tanhf(in_now / cap);
+            fg = log_sigmoid(cap * tanhf(f_now / cap));
+        }
         float m_before = 0.f, m_mine = 0.f;
-        for (int s = 0; s < n_here; ++s) {
+#pragma unroll
+        for (int s = 0; s < 32; ++s) {                        // (the shuffles do not wait for the chain: only add and max do)
             const float fi = __shfl_sync(0xffffffffu, ig, s);
             const float ff = __shfl_sync(0xffffffffu, fg, s);
             const float m_new = fmaxf(ff + m, fi);
