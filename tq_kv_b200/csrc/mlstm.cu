@@ -108,14 +108,22 @@ mlstm_read_kernel(const float* __restrict__ o, int ea, int e, const float* __res
     pdl_wait();
     pdl_launch();
     const float* row = o + (size_t)p * ea;
-    const float m = scal[(size_t)p * 4 + 2];
-    const float den = fmaxf(fabsf(row[e] * q_scale), expf(-m)) + floor_;
-    float v[MR_MAX_PER_LANE];
-    float ss = 0.f;
+    // every load of the warp is asked for at once: the values, their gates, n . q and m
+    float v[MR_MAX_PER_LANE], g[MR_MAX_PER_LANE];
 #pragma unroll
     for (int i = 0; i < MR_MAX_PER_LANE; ++i) {
         const int j = lane + 32 * i;
-        v[i] = j < e ? row[j] * q_scale / den : 0.f;
+        v[i] = j < e ? row[j] : 0.f;
+        g[i] = j < e ? gate[(size_t)t * ldg + h * e + j] : 0.f;
+    }
+    const float nq = row[e];
+    const float m = scal[(size_t)p * 4 + 2];
+    const float den = fmaxf(fabsf(nq * q_scale), expf(-m)) + floor_;
+    const float by_den = q_scale / den;               // one division per (token, head)
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MR_MAX_PER_LANE; ++i) {
+        v[i] *= by_den;
         ss = fmaf(v[i], v[i], ss);
     }
     ss = warp_sum(ss);
@@ -125,8 +133,9 @@ mlstm_read_kernel(const float* __restrict__ o, int ea, int e, const float* __res
         const int j = lane + 32 * i;
         if (j < e) {
             const int c = h * e + j;
-            const float g = gate[(size_t)t * ldg + c];
-            out[(size_t)t * H * e + c] = from_f32<TO>(v[i] * inv * norm_w[c] / (1.f + expf(-g)));
+            // (a bfloat16 result keeps 8 bits: the fast exponential and division do)
+            const float sg = sizeof(TO) == 2 ? __fdividef(1.f, 1.f + __expf(-g[i])) : 1.f / (1.f + expf(-g[i]));
+            out[(size_t)t * H * e + c] = from_f32<TO>(v[i] * inv * norm_w[c] * sg);
         }
     }
 }
