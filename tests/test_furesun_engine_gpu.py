@@ -230,6 +230,33 @@ def test_greedy_generation_through_the_entry_point_and_the_command_line(tmp_root
     assert [int(t) for t in p.stdout.strip().splitlines()[-1].split(",")] == want[1]
 
 
+def test_greedy_generation_of_a_model_without_a_memory(tmp_root):
+    """Without a mixer that keeps state the engine pads whole prompts to the sizes of captured graphs: the padded
+    rows must reach neither a cache, nor the keys a later layer borrows, nor a real row's result."""
+    import tq_kv_b200 as tq
+    from furesun_cases import attn, dense, latent, make_weights, model, moe
+    cfg = model(210, 96, 1e-6, [
+        {**attn(4, 2, 24, 16, 40, 0.2, cap=20.0, dims=12), "mlp": moe(48, 4, 2, 1.5, shared=40)},
+        {**latent(2, 16, 8, 24, 40, 50, 0.2, scaling=(4.0, 64, 16.0, 2.0)), "mlp": dense(120)},
+        {**attn(4, 2, 24, 16, 70, 0.2, cap=20.0, dims=12, kv_from=0), "mlp": None},
+    ], cap=20.0)
+    path = pf.write_folder(os.path.join(str(tmp_root), "no_memory"), cfg, make_weights(cfg, 31))
+    c, w = pf.read_folder(path)
+    prompts = [tokens(n, cfg["vocab"], 500 + n) for n in (1, 5, 63, 64, 65, 130)]
+    want = [pf.greedy(c, w, p, 12) for p in prompts]
+    eng = tq.load(path, dtype="float32", max_batch=3, max_context=256)
+    assert eng.model.padded_rows_ok
+    for group in (prompts[:3], prompts[3:], prompts[5:]):                 # batches of three, and a prompt alone
+        res = eng.generate(group, tq.GenerationParams.greedy(12, stop_token_ids=()))
+        for r, p in zip(res, group):
+            wt = want[prompts.index(p)]
+            n = next((i for i, (x, y) in enumerate(zip(r.tokens, wt)) if x != y), 12)
+            if n < 12:                                                      # a tie within float32 rounding, or a fault
+                row = pf.decoder(c, w, p + wt[:n])[-1]
+                assert abs(float(row[r.tokens[n]] - row[wt[n]])) < 1e-4 * float(row.abs().max()), (len(p), n, r.tokens, wt)
+    assert eng.cache.free_slots == 3
+
+
 def test_greedy_generation_past_the_windows_with_requests_that_wait_for_a_slot(tmp_root):
     """Five requests on two slots: each generates far past the windows of the model; the scheduler gives freed
     slots, pages and states to the waiting ones."""
